@@ -3,6 +3,7 @@ from .registry import config_class_for, read_config, register_architecture, regi
 from .llama import LlamaConfig
 from .sagizen import SagizenConfig
 from .vosulorn import VosulornConfig
+from .redenex import RedenexConfig
 
 __all__ = ["ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "config_class_for", "read_config",
-           "register_architecture", "registered_architectures", "LlamaConfig", "SagizenConfig", "VosulornConfig"]
+           "register_architecture", "registered_architectures", "LlamaConfig", "SagizenConfig", "VosulornConfig", "RedenexConfig"]

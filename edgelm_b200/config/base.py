@@ -76,6 +76,7 @@ class ModelPlan:
     head: PartSpec
     stop_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
+    residual_streams: int = 1      # copies of the residual stream that the layers carry (their arrangement reads and writes all of them)
 
     def first_runs(self, n):
         """The same plan cut to its first `n` schedule entries (and the layers they name): a shallower model of the
@@ -93,6 +94,8 @@ class ModelPlan:
     def validate(self):
         if not self.layers or not self.schedule:
             raise ConfigError("a model needs at least one layer and one schedule entry")
+        if self.residual_streams < 1:
+            raise ConfigError(f"{self.residual_streams} residual streams")
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError(f"schedule entry {i} names layer {e.layer}; there are {len(self.layers)}")

@@ -53,13 +53,17 @@ __device__ __forceinline__ float rotated(const float* x, int i, int rot, int int
 constexpr int MA_WARPS = 4;
 
 // qkv [tokens][H dk + G dk + G dv] float32 (+ bias): the first `rot` dimensions of every query and key head rotated;
-// queries to q_out [tokens][H][dk] float32, keys and values into their cache rows.
+// queries to q_out [tokens][H][dk] float32, keys and values into their cache rows.  A head may be `maps` runs of dk / maps
+// dimensions side by side (the maps of a differential attention): then each run is rotated by itself.  With `q_norm` /
+// `k_norm` (dk / maps weights each, shared by all heads and runs) every run is first divided by its root mean square
+// (eps inside the root) and multiplied by the weight.
 template <typename T>
 __global__ void __launch_bounds__(MA_WARPS * 32)
 rotate_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, float* __restrict__ q_out,
                      const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table,
                      int table_stride, int n_pages, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int dk, int dv,
-                     int rot, int interleaved, const double* __restrict__ freq, int* __restrict__ err) {
+                     int rot, int interleaved, const double* __restrict__ freq, int* __restrict__ err, int maps,
+                     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float ra_stage[];   // MA_WARPS rows of dk floats
@@ -83,8 +87,21 @@ rotate_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bi
     const float* b = bias ? bias + (size_t)head * dk : nullptr;
     for (int i = lane; i < dk; i += 32) sh[i] = src[i] + (b ? b[i] : 0.f);
     __syncwarp();
+    const int ds = dk / maps;
+    const float* nw = head < H ? q_norm : k_norm;
+    if (nw) {
+      for (int mp = 0; mp < maps; ++mp) {
+        float* run = sh + mp * ds;
+        float ss = 0.f;
+        for (int i = lane; i < ds; i += 32) ss = fmaf(run[i], run[i], ss);
+        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)ds + eps);
+        for (int i = lane; i < ds; i += 32) run[i] = run[i] * inv * nw[i];
+      }
+      __syncwarp();
+    }
     for (int i = lane; i < dk; i += 32) {
-      const float x = i < rot ? rotated(sh, i, rot, interleaved, (double)pos, freq) : sh[i];
+      const int mp = i / ds, j = i - mp * ds;
+      const float x = j < rot ? rotated(sh + mp * ds, j, rot, interleaved, (double)pos, freq) : sh[i];
       if (head < H) q_out[((size_t)t * H + head) * dk + i] = x;
       else kcache[(((size_t)page * G + (head - H)) * PAGE + in_page) * dk + i] = from_f32<T>(x);
     }
@@ -258,7 +275,7 @@ __global__ void __launch_bounds__(MA_MAX_WARPS * 32)
 masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vbase, int ldv,
                    const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table,
                    int table_stride, int n_pages, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
-                   const float* __restrict__ sink, int vec_k) {
+                   const float* __restrict__ sink, int vec_k, int maps) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float ma_smem[];
@@ -270,9 +287,12 @@ masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* _
   float* wo = wl + NW;             // [NW][dv]
   const int pos = tok_pos[t];
   if (pos < 0) return;
-  const int g = h / (H / G);
+  // `maps` > 1: a head is `maps` runs of dk dimensions side by side, in the queries and in a key row; each run is an
+  // attention of its own over the head's values.  blockIdx.y = head * maps + run.
+  const int HV = H * maps, kp = dk * maps, koff = (h % maps) * dk;
+  const int g = (h / maps) / (H / G);
   const int32_t* table = page_table + (size_t)tok_seq[t] * table_stride;
-  const float* qrow = q + ((size_t)t * H + h) * dk;
+  const float* qrow = q + ((size_t)t * HV + h) * dk;
   for (int i = threadIdx.x; i < dk; i += blockDim.x) qh[i] = qrow[i] * scale;
   __syncthreads();
   const int lo = first_key(pos, mask, mask_size), n_keys = pos - lo + 1;
@@ -290,7 +310,7 @@ masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* _
       const int page = table[p / PAGE];
       if (page >= 0 && page < n_pages) {
         vrow = (page * G + g) * PAGE + p % PAGE;
-        sc = ma_dot(qh, kcache + (size_t)vrow * dk, dk, vec_k != 0);
+        sc = ma_dot(qh, kcache + (size_t)vrow * kp + koff, dk, vec_k != 0);
       }
     }
     const float m_new = fmaxf(m, warp_max(sc));
@@ -321,16 +341,16 @@ masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* _
     if (d < dv) wo[warp * dv + d] = o[r];
   }
   __syncthreads();
-  float M = sink ? sink[h] : -INFINITY;
+  float M = sink ? sink[h / maps] : -INFINITY;
   for (int w2 = 0; w2 < NW; ++w2) M = fmaxf(M, wm[w2]);
-  float L = sink ? expf(sink[h] - M) : 0.f;
+  float L = sink ? expf(sink[h / maps] - M) : 0.f;
   for (int w2 = 0; w2 < NW; ++w2) L += wm[w2] == -INFINITY ? 0.f : wl[w2] * expf(wm[w2] - M);
   const float inv = L > 0.f ? 1.0f / L : 0.f;
   for (int d = threadIdx.x; d < dv; d += blockDim.x) {
     float acc = 0.f;
     for (int w2 = 0; w2 < NW; ++w2)
       if (wm[w2] != -INFINITY) acc = fmaf(wo[w2 * dv + d], expf(wm[w2] - M), acc);
-    out[((size_t)t * H + h) * dv + d] = from_f32<TO>(acc * inv);
+    out[((size_t)t * HV + h) * dv + d] = from_f32<TO>(acc * inv);
   }
 }
 
@@ -383,7 +403,7 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
                          const int32_t* __restrict__ page_table, int table_stride, int n_pages, const int32_t* __restrict__ tile_seq,
                          const int32_t* __restrict__ tile_tok0, const int32_t* __restrict__ tile_ntok, const int32_t* __restrict__ tile_pos0,
                          int H, int G, int dk, int dv, float scale, int mask, int mask_size, const float* __restrict__ sink,
-                         int n_splits, float* __restrict__ part) {
+                         int n_splits, float* __restrict__ part, int maps) {
   extern __shared__ float tm_smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -394,14 +414,16 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
   float* Vs = own_v ? Ks + TM_KEYS * ks : Ks;   // [TM_KEYS][dv]
   float* Qs = Ks + TM_KEYS * ks + (own_v ? TM_KEYS * dv : 0);   // [TM_ROWS][dk]
   float* Ps = Qs + TM_ROWS * dk;                // [TM_ROWS][TM_KEYS]
-  const int tile = blockIdx.x, g = blockIdx.y, grp = H / G;
+  // `maps` > 1: a head is `maps` runs of dk dimensions side by side (queries and key rows); blockIdx.y = kv head * maps + run,
+  // and the block's rows are the run's queries of the heads that share the kv head.  Row (token, head, run) of q and out.
+  const int tile = blockIdx.x, g = blockIdx.y / maps, mp = blockIdx.y % maps, grp = H / G, HV = H * maps, kfull = dk * maps;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int seq = tile_seq[tile], tok0 = tile_tok0[tile], ntok = tile_ntok[tile], pos0 = tile_pos0[tile];
   // `page_table` null: the keys and values are the step's own rows [token][kv_head][dk or dv] (every sequence of the step
   // starts at position 0, so position p of the tile's sequence is packed row tok0 - pos0 + p)
   const bool paged = page_table != nullptr;
   const int32_t* pages = paged ? page_table + (size_t)seq * table_stride : nullptr;
-  const int k_pitch = paged ? dk : G * dk, v_pitch = paged ? dv : G * dv;
+  const int k_pitch = paged ? kfull : G * kfull, v_pitch = paged ? dv : G * dv;
   // n_splits > 1: the pages a tile's rows see are dealt to n_splits blocks (blockIdx.z = row tile * n_splits + split); each
   // leaves its rows' maximum, denominator and weighted values in `part` [token][head][split][2 + dv] and `masked_attn_fold`
   // merges them: steps of one token a sequence whose query heads share few key heads
@@ -413,7 +435,7 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
   for (int i = threadIdx.x; i < TM_ROWS * dk; i += blockDim.x) {
     const int r = i / dk, d = i - r * dk;
     const int rr = row_base + r, tok = rr / grp, head = g * grp + rr % grp;
-    Qs[i] = r < rows_here ? q[((size_t)(tok0 + tok) * H + head) * dk + d] : 0.f;
+    Qs[i] = r < rows_here ? q[((size_t)(tok0 + tok) * HV + head * maps + mp) * dk + d] : 0.f;
   }
   float m[TM_RW], l[TM_RW], acc[TM_RW][NC];
   int limit[TM_RW], first[TM_RW];
@@ -437,7 +459,7 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
     const int page = paged ? pages[kt] : 0;
     const bool held = !paged || (page >= 0 && page < n_pages);
     const size_t first_row = paged ? ((size_t)(held ? page : 0) * G + g) * PAGE : ((size_t)(tok0 - pos0 + kt * PAGE) * G + g);
-    const T* kp = kcache + first_row * dk;
+    const T* kp = kcache + first_row * kfull + mp * dk;
     const int valid = held ? min(PAGE, last_pos + 1 - kt * PAGE) : 0;   // rows of the page that hold this block's keys
     __syncthreads();
     stage_rows<T>(Ks, ks, kp, k_pitch, dk, valid);      // what lies behind `valid` is not this sequence's: never let it in
@@ -509,7 +531,7 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
     if (rr >= rows_total) continue;
     const int tok = rr / grp, head = g * grp + rr % grp;
     if (n_splits > 1) {
-      float* dst = part + (((size_t)(tok0 + tok) * H + head) * n_splits + split) * (2 + dv);
+      float* dst = part + (((size_t)(tok0 + tok) * HV + head * maps + mp) * n_splits + split) * (2 + dv);
       if (lane == 0) { dst[0] = m[r]; dst[1] = l[r]; }
 #pragma unroll
       for (int c = 0; c < NC; ++c) {
@@ -528,7 +550,7 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
       const int d = lane + 32 * c;
-      if (d < dv) out[((size_t)(tok0 + tok) * H + head) * dv + d] = from_f32<TO>(acc[r][c] * inv);
+      if (d < dv) out[((size_t)(tok0 + tok) * HV + head * maps + mp) * dv + d] = from_f32<TO>(acc[r][c] * inv);
     }
   }
 }
@@ -559,15 +581,54 @@ __global__ void masked_attn_fold_kernel(const float* __restrict__ part, TO* __re
   }
 }
 
+// Two attention maps of a head into one ("differential" attention): a [tokens][H][2][dv] float32;
+// o = a_1 - lambda a_2, then o / sqrt(mean(o^2) + eps) over the head's dv values, times `post` (and `w` [dv], if given).
+// A warp per (token, head).
+template <typename TO>
+__global__ void __launch_bounds__(128)
+diff_combine_kernel(const float* __restrict__ a, TO* __restrict__ out, float lambda, float eps, float post, const float* __restrict__ w,
+                    int n_rows, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  const float* a1 = a + (size_t)row * 2 * dv;
+  const float* a2 = a1 + dv;
+  float ss = 0.f;
+  for (int d = lane; d < dv; d += 32) {
+    const float o = a1[d] - lambda * a2[d];
+    ss = fmaf(o, o, ss);
+  }
+  const float inv = post / sqrtf(warp_sum(ss) / (float)dv + eps);
+  for (int d = lane; d < dv; d += 32) {
+    const float o = a1[d] - lambda * a2[d];
+    out[(size_t)row * dv + d] = from_f32<TO>(o * inv * (w ? w[d] : 1.0f));
+  }
+}
+
 }  // namespace edgelm
 
 using namespace edgelm;
 
+extern "C" int edgelm_diff_combine(const float* a, void* out, int out_dtype, float lambda, float eps, float post, const float* w, int n_rows,
+                                   int dv, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  EL_REFUSE(n_rows > 0 && dv >= 1, "diff_combine: bad sizes");
+  const dim3 grid((n_rows + 3) / 4), block(128);
+  const int bit = pdl_bit_for_tokens(n_rows);
+  if (out_dtype == DT_F32) launch_pdl(bit, diff_combine_kernel<float>, grid, block, (size_t)0, stream, a, (float*)out, lambda, eps, post, w, n_rows, dv);
+  else if (out_dtype == DT_BF16) launch_pdl(bit, diff_combine_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, a, (__nv_bfloat16*)out, lambda, eps, post, w, n_rows, dv);
+  else EL_REFUSE(false, "diff_combine: unknown dtype code %d", out_dtype);
+  EL_LAUNCH_CHECK("diff_combine");
+  return 0;
+}
+
 extern "C" int edgelm_rotate_append(const float* qkv, const float* bias, float* q_out, const int32_t* tok_pos, const int32_t* tok_seq,
                                     const int32_t* page_table, int table_stride, int n_pages, void* kcache, void* vcache, int dtype,
                                     int n_tokens, int H, int G, int dk, int dv, int rot, int interleaved, const double* freq, int* err,
-                                    cudaStream_t stream) {
+                                    int maps, const float* q_norm, const float* k_norm, float eps, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
+  EL_REFUSE(maps >= 1 && dk % maps == 0 && rot <= dk / maps, "rotate_append: %d maps of a head of %d with %d rotated dimensions", maps, dk, rot);
   EL_REFUSE(n_tokens > 0 && H > 0 && G > 0 && H % G == 0, "rotate_append: %d query heads over %d key/value heads", H, G);
   EL_REFUSE(dk >= 1 && dk <= 2048 && dv >= 1, "rotate_append: head sizes %d / %d are not taken", dk, dv);
   EL_REFUSE(rot >= 0 && rot <= dk && rot % 2 == 0 && (rot == 0 || freq != nullptr), "rotate_append: %d rotated dimensions of %d", rot, dk);
@@ -576,10 +637,10 @@ extern "C" int edgelm_rotate_append(const float* qkv, const float* bias, float* 
   const int bit = pdl_bit_for_tokens(n_tokens);
   if (dtype == DT_F32)
     launch_pdl(bit, rotate_append_kernel<float>, grid, block, smem, stream, qkv, bias, q_out, tok_pos, tok_seq, page_table, table_stride,
-               n_pages, (float*)kcache, (float*)vcache, H, G, dk, dv, rot, interleaved, freq, err);
+               n_pages, (float*)kcache, (float*)vcache, H, G, dk, dv, rot, interleaved, freq, err, maps, q_norm, k_norm, eps);
   else if (dtype == DT_BF16)
     launch_pdl(bit, rotate_append_kernel<__nv_bfloat16>, grid, block, smem, stream, qkv, bias, q_out, tok_pos, tok_seq, page_table,
-               table_stride, n_pages, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, H, G, dk, dv, rot, interleaved, freq, err);
+               table_stride, n_pages, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, H, G, dk, dv, rot, interleaved, freq, err, maps, q_norm, k_norm, eps);
   else
     EL_REFUSE(false, "rotate_append: unknown dtype code %d", dtype);
   EL_LAUNCH_CHECK("rotate_append");
@@ -662,28 +723,30 @@ static int masked_common_check(const char* what, int H, int G, int dk, int dv, i
 template <typename T, typename TO, int DVR>
 static void launch_masked(const float* q, void* out, const void* kcache, const void* vcache, const int32_t* tok_pos, const int32_t* tok_seq,
                           const int32_t* page_table, int table_stride, int n_pages, int n_tokens, int H, int G, int dk, int dv, float scale,
-                          int mask, int mask_size, const float* sink, int warps, cudaStream_t stream) {
+                          int mask, int mask_size, const float* sink, int warps, int maps, cudaStream_t stream) {
   const T* vb = vcache ? (const T*)vcache : (const T*)kcache;
   const int ldv = vcache ? dv : dk;
   const int vec_k = (dk % (16 / (int)sizeof(T)) == 0) && ((uintptr_t)kcache % 16 == 0);
   const size_t smem = ((size_t)((dk + 3) & ~3) + (size_t)warps * (2 + dv)) * sizeof(float);
   auto kern = masked_attn_kernel<T, TO, DVR>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  launch_pdl(pdl_bit_for_tokens(n_tokens), kern, dim3(n_tokens, H), dim3(warps * 32), smem, stream, q, (TO*)out, (const T*)kcache, vb, ldv,
-             tok_pos, tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, mask, mask_size, sink, vec_k);
+  launch_pdl(pdl_bit_for_tokens(n_tokens), kern, dim3(n_tokens, H * maps), dim3(warps * 32), smem, stream, q, (TO*)out, (const T*)kcache, vb, ldv,
+             tok_pos, tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, mask, mask_size, sink, vec_k, maps);
 }
 
 // `vcache` null: the values are the first dv dimensions of the key rows.  `max_keys`: the most keys a token of the step sees
-// (chooses how many warps share a token's keys).
+// (chooses how many warps share a token's keys).  `maps` > 1: every query head and key row holds `maps` runs of dk dimensions,
+// each an attention of its own over the head's values; q [tokens][H][maps][dk], out [tokens][H][maps][dv].
 extern "C" int edgelm_masked_attn(const float* q, void* out, int out_dtype, const void* kcache, const void* vcache, int dtype,
                                   const int32_t* tok_pos, const int32_t* tok_seq, const int32_t* page_table, int table_stride, int n_pages,
                                   int n_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size, const float* sink,
-                                  int max_keys, cudaStream_t stream) {
+                                  int max_keys, int maps, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   if (masked_common_check("masked_attn", H, G, dk, dv, mask, mask_size, dtype, out_dtype)) return -1;
+  EL_REFUSE(maps >= 1 && H * maps <= 65535 && (maps == 1 || (sink == nullptr && vcache != nullptr)), "masked_attn: %d maps take no sink and values of their own", maps);
   EL_REFUSE(vcache != nullptr || dv <= dk, "masked_attn: values of %d inside keys of %d", dv, dk);
   const int warps = max_keys <= 64 ? 2 : (max_keys <= 256 ? 4 : MA_MAX_WARPS);
-#define EL_MA2(T, TO, DVR) launch_masked<T, TO, DVR>(q, out, kcache, vcache, tok_pos, tok_seq, page_table, table_stride, n_pages, n_tokens, H, G, dk, dv, scale, mask, mask_size, sink, warps, stream)
+#define EL_MA2(T, TO, DVR) launch_masked<T, TO, DVR>(q, out, kcache, vcache, tok_pos, tok_seq, page_table, table_stride, n_pages, n_tokens, H, G, dk, dv, scale, mask, mask_size, sink, warps, maps, stream)
 #define EL_MA(DVR) do { if (dtype == DT_F32) EL_MA2(float, float, DVR); else if (out_dtype == DT_F32) EL_MA2(__nv_bfloat16, float, DVR); else EL_MA2(__nv_bfloat16, __nv_bfloat16, DVR); } while (0)
   if (dv <= 32) EL_MA(1); else if (dv <= 64) EL_MA(2); else if (dv <= 128) EL_MA(4); else if (dv <= 256) EL_MA(8); else EL_MA(16);
 #undef EL_MA
@@ -696,20 +759,20 @@ template <typename T, typename TO, int NC>
 static int launch_masked_tiled(const float* q, void* out, const void* kcache, const void* vcache, const int32_t* page_table, int table_stride,
                                int n_pages, const int32_t* tile_seq, const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0,
                                int n_tiles, int max_tile_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
-                               const float* sink, int n_splits, float* part, int n_tokens, cudaStream_t stream) {
+                               const float* sink, int n_splits, float* part, int n_tokens, int maps, cudaStream_t stream) {
   const size_t smem = ((size_t)TM_KEYS * (dk + 1) + (vcache ? (size_t)TM_KEYS * dv : 0) + (size_t)TM_ROWS * dk + (size_t)TM_ROWS * TM_KEYS) * sizeof(float);
   EL_REFUSE(smem <= 227 * 1024, "masked_attn_tiled: heads of %d / %d need %zu bytes of shared memory", dk, dv, smem);
   auto kern = masked_attn_tiled_kernel<T, TO, NC>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const int grp = H / G;
-  const dim3 grid(n_tiles, G, ((max_tile_tokens * grp + TM_ROWS - 1) / TM_ROWS) * n_splits);
+  const dim3 grid(n_tiles, G * maps, ((max_tile_tokens * grp + TM_ROWS - 1) / TM_ROWS) * n_splits);
   const int bit = pdl_bit_for_tokens(n_tokens);
   launch_pdl(bit, kern, grid, dim3(TM_WARPS * 32), smem, stream, q, (TO*)out, (const T*)kcache, (const T*)vcache, page_table, table_stride, n_pages,
-             tile_seq, tile_tok0, tile_ntok, tile_pos0, H, G, dk, dv, scale, mask, mask_size, sink, n_splits, part);
+             tile_seq, tile_tok0, tile_ntok, tile_pos0, H, G, dk, dv, scale, mask, mask_size, sink, n_splits, part, maps);
   if (n_splits > 1) {
     if (cudaGetLastError() != cudaSuccess) return 0;   // (the caller reports it)
-    launch_pdl(bit, masked_attn_fold_kernel<TO>, dim3(n_tokens, H), dim3(dv >= 256 ? 256 : 128), (size_t)0, stream, (const float*)part, (TO*)out, sink, H, dv,
-               n_splits);
+    launch_pdl(bit, masked_attn_fold_kernel<TO>, dim3(n_tokens, H * maps), dim3(dv >= 256 ? 256 : 128), (size_t)0, stream, (const float*)part, (TO*)out, sink,
+               H * maps, dv, n_splits);
   }
   return 0;
 }
@@ -718,14 +781,15 @@ extern "C" int edgelm_masked_attn_tiled(const float* q, void* out, int out_dtype
                                         const int32_t* page_table, int table_stride, int n_pages, const int32_t* tile_seq,
                                         const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0, int n_tiles,
                                         int max_tile_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
-                                        const float* sink, int n_splits, float* part, int n_tokens, cudaStream_t stream) {
+                                        const float* sink, int n_splits, float* part, int n_tokens, int maps, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
+  EL_REFUSE(maps >= 1 && G * maps <= 65535 && (maps == 1 || (sink == nullptr && vcache != nullptr)), "masked_attn_tiled: %d maps take no sink and values of their own", maps);
   EL_REFUSE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || part != nullptr) && n_tokens > 0, "masked_attn_tiled: %d splits", n_splits);
   if (masked_common_check("masked_attn_tiled", H, G, dk, dv, mask, mask_size, dtype, out_dtype)) return -1;
   EL_REFUSE(n_tiles > 0 && max_tile_tokens > 0 && G <= 65535, "masked_attn_tiled: bad tile counts");
   EL_REFUSE(vcache != nullptr || dv <= dk, "masked_attn_tiled: values of %d inside keys of %d", dv, dk);
   int rc = 0;
-#define EL_MT2(T, TO, NC) rc = launch_masked_tiled<T, TO, NC>(q, out, kcache, vcache, page_table, table_stride, n_pages, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, H, G, dk, dv, scale, mask, mask_size, sink, n_splits, part, n_tokens, stream)
+#define EL_MT2(T, TO, NC) rc = launch_masked_tiled<T, TO, NC>(q, out, kcache, vcache, page_table, table_stride, n_pages, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, H, G, dk, dv, scale, mask, mask_size, sink, n_splits, part, n_tokens, maps, stream)
 #define EL_MT(NC) do { if (dtype == DT_F32) EL_MT2(float, float, NC); else if (out_dtype == DT_F32) EL_MT2(__nv_bfloat16, float, NC); else EL_MT2(__nv_bfloat16, __nv_bfloat16, NC); } while (0)
   if (dv <= 32) EL_MT(1); else if (dv <= 64) EL_MT(2); else if (dv <= 128) EL_MT(4); else if (dv <= 256) EL_MT(8); else EL_MT(16);
 #undef EL_MT

@@ -480,13 +480,24 @@ def conv_silu(u, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, n_seqs, upd
     """Causal convolution over the channels u[:, off : off + C] with taps w [C, taps] and bias b, then silu; the inputs
     before the step come from state [slots, taps - 1, C], which is then moved on to the step's last inputs (with
     `update_state` False that is left to the caller: `ssm_scan` does it when it is handed the state)."""
-    for t, n in ((u, "u"), (w, "w"), (b, "b"), (state, "state"), (out, "out")):
+    conv_act(u, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, n_seqs, update_state=update_state, act="silu")
+
+
+def conv_act(u, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, n_seqs, update_state=True, in_bias=None, act=None):
+    """`conv_silu` with its options: `b` may be None (no bias on the result); `in_bias` [C] is added to every input that `u`
+    brings before the convolution (a projection's bias: the state then keeps inputs with it, and what lies before a
+    sequence's start stays zero); `act` None (the sum itself) or "silu"."""
+    for t, n in ((u, "u"), (w, "w"), (state, "state"), (out, "out")):
         _f32(t, n)
     T, C = out.shape
     taps = w.shape[1]
-    _need(u.shape[0] == T and w.shape[0] == C and b.numel() == C and tuple(state.shape[1:]) == (taps - 1, C), "conv_silu: shapes")
-    _check(lib().edgelm_conv_silu(_p(u), u.stride(0), int(off), _p(w), _p(b), _p(state), _p(out), _p(tok_seq), _p(seq_tok0), _p(seq_slot),
-                                  T, int(n_seqs), C, taps, 1 if update_state else 0, _stream()), launches=2 if taps > 1 and update_state else 1)
+    _need(act in (None, "silu"), "conv_act: activation")
+    _need(u.shape[0] == T and w.shape[0] == C and tuple(state.shape[1:]) == (taps - 1, C), "conv_act: shapes")
+    for t, n in ((b, "b"), (in_bias, "in_bias")):
+        _need(t is None or (t.dtype == torch.float32 and t.is_cuda and t.is_contiguous() and t.numel() == C), f"conv_act: {n}")
+    _check(lib().edgelm_conv_act(_p(u), u.stride(0), int(off), _p(w), _p(b), _p(state), _p(out), _p(tok_seq), _p(seq_tok0), _p(seq_slot),
+                                 T, int(n_seqs), C, taps, 1 if update_state else 0, _p(in_bias), 1 if act == "silu" else 0, _stream()),
+           launches=2 if taps > 1 and update_state else 1)
 
 
 def ssm_scan(xbc, u, dt_off, dt_bias, a_log, d, state, y, seq_tok0, seq_slot, n_seqs, heads, groups, n_state, head_dim,
@@ -641,10 +652,13 @@ def _masked_cache_check(kcache, vcache, nkv, dk, dv, what):
         _need(dv <= dk, f"{what}: values of {dv} dimensions inside keys of {dk}")
 
 
-def rotate_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache, nh, nkv, dk, dv, rot, interleaved, freq, err):
+def rotate_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache, nh, nkv, dk, dv, rot, interleaved, freq, err,
+                  maps=1, q_norm=None, k_norm=None, eps=0.0):
     """qkv [T, nh dk + nkv dk + nkv dv] float32 (+ bias): the first `rot` dimensions of every query and key head are rotated
     by position * freq (float64 frequencies; pairs (2i, 2i + 1) if `interleaved`, else (i, i + rot/2)); queries go to q_out
-    [T, nh dk] float32, keys and values to their places in the cache pages."""
+    [T, nh dk] float32, keys and values to their places in the cache pages.  `maps` > 1: a head of dk dimensions is `maps`
+    runs of dk / maps side by side, each rotated (its first `rot` dimensions) by itself.  `q_norm` / `k_norm` (float32
+    [dk / maps]): every run is first divided by its root mean square (`eps` inside the root) and multiplied by the weight."""
     _f32(qkv, "qkv"); _f32(q_out, "q_out")
     T = qkv.shape[0]
     _need(qkv.shape[1] == (nh + nkv) * dk + nkv * dv and q_out.shape == (T, nh * dk), "rotate_append: shapes")
@@ -652,11 +666,15 @@ def rotate_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache
     _need(rot == 0 or (freq is not None and freq.dtype == torch.float64 and freq.numel() == rot // 2 and freq.is_contiguous()), "rotate_append: frequencies")
     _masked_cache_check(kcache, vcache, nkv, dk, dv, "rotate_append")
     _need(vcache is not None, "rotate_append: values need a cache of their own")
+    _need(maps >= 1 and dk % maps == 0 and rot <= dk // maps, "rotate_append: the maps of a head")
+    for w, n in ((q_norm, "q_norm"), (k_norm, "k_norm")):
+        _need(w is None or (w.dtype == torch.float32 and w.is_cuda and w.is_contiguous() and w.numel() == dk // maps), f"rotate_append: {n}")
     for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (page_table, "page_table")):
         _i32(t, n)
     _check(lib().edgelm_rotate_append(_p(qkv), _p(bias), _p(q_out), _p(tok_pos), _p(tok_seq), _p(page_table), page_table.stride(0),
                                       kcache.shape[0], _p(kcache), _p(vcache), _dt(kcache), T, nh, nkv, dk, dv, int(rot),
-                                      1 if interleaved else 0, _p(freq), _p(err), _stream()))
+                                      1 if interleaved else 0, _p(freq), _p(err), int(maps), _p(q_norm), _p(k_norm), ctypes.c_float(eps),
+                                      _stream()))
 
 
 def latent_prepare(u, kv_off, has_kv, q_out, q_pitch, q_off, copy_q, norm_w, eps, tok_pos, tok_seq, page_table, kcache, nh, d, rd, r, freq, err,
@@ -710,41 +728,46 @@ def add_row_bias(x, b):
     _check(lib().edgelm_add_row_bias(_p(x), _p(b), x.shape[0], x.shape[1], _stream()))
 
 
-def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, dk, dv, scale, mask, mask_size, sink, max_keys):
+def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, dk, dv, scale, mask, mask_size, sink, max_keys, maps=1):
     """Attention of every token of the step over the keys lo .. its position (`mask`: MASK_CAUSAL lo = 0; MASK_WINDOW the
     last `mask_size` keys; MASK_CHUNK the keys of its own chunk of `mask_size` positions).  q [T, nh dk] float32; out
     [T, nh dv] float32 or the cache's type; `vcache` None: a value is the first dv dimensions of its key row.  `sink`
-    (float32 [nh] or None): one more term exp(sink_h) in the denominator.  `max_keys`: the most keys a token sees."""
+    (float32 [nh] or None): one more term exp(sink_h) in the denominator.  `max_keys`: the most keys a token sees.
+    `maps` > 1: every query head and key row holds `maps` runs of dk dimensions, each an attention of its own over the
+    head's values: q [T, nh maps dk], key rows of maps dk, out [T, nh maps dv] (no sink then)."""
     _f32(q, "q")
     T = q.shape[0]
-    _need(q.shape == (T, nh * dk) and out.is_contiguous() and out.shape == (T, nh * dv), "masked_attn: shapes")
-    _masked_cache_check(kcache, vcache, nkv, dk, dv, "masked_attn")
+    _need(q.shape == (T, nh * maps * dk) and out.is_contiguous() and out.shape == (T, nh * maps * dv), "masked_attn: shapes")
+    _need(maps == 1 or (sink is None and vcache is not None), "masked_attn: several maps take no sink and values of their own")
+    _masked_cache_check(kcache, vcache, nkv, dk * maps, dv, "masked_attn")
     _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh), "masked_attn: sink")
     for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (page_table, "page_table")):
         _i32(t, n)
     _check(lib().edgelm_masked_attn(_p(q), _p(out), _dt(out), _p(kcache), _p(vcache), _dt(kcache), _p(tok_pos), _p(tok_seq), _p(page_table),
                                     page_table.stride(0), kcache.shape[0], T, nh, nkv, dk, dv, ctypes.c_float(scale), int(mask), int(mask_size or 0),
-                                    _p(sink), int(max_keys), _stream()))
+                                    _p(sink), int(max_keys), int(maps), _stream()))
 
 
 def masked_attn_tiled(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, nh, nkv,
-                      dk, dv, scale, mask, mask_size, sink, n_splits=1, part=None):
+                      dk, dv, scale, mask, mask_size, sink, n_splits=1, part=None, maps=1):
     """`masked_attn` for prompt steps: the step's tokens come as tiles (runs of at most `max_tile_tokens` consecutive tokens of
     one sequence); a page of keys and values is staged once for all the rows of a tile.  `page_table` None: `kcache` [T, nkv dk]
     and `vcache` [T, nkv dv] are the step's own keys and values, and every sequence of the step starts at position 0.
     `n_splits` > 1: the pages that a tile sees are dealt to so many blocks, whose partial results go through `part` (float32,
-    T nh n_splits (2 + dv) values) and are merged by a second launch: for steps of few tokens over long sequences."""
+    T nh n_splits (2 + dv) values) and are merged by a second launch: for steps of few tokens over long sequences.
+    `maps` as in `masked_attn` (then `part` holds T nh maps n_splits (2 + dv) values)."""
     _f32(q, "q")
     T = q.shape[0]
-    _need(q.shape == (T, nh * dk) and out.is_contiguous() and out.shape == (T, nh * dv), "masked_attn_tiled: shapes")
+    _need(q.shape == (T, nh * maps * dk) and out.is_contiguous() and out.shape == (T, nh * maps * dv), "masked_attn_tiled: shapes")
+    _need(maps == 1 or (sink is None and vcache is not None), "masked_attn_tiled: several maps take no sink and values of their own")
     if page_table is not None:
-        _masked_cache_check(kcache, vcache, nkv, dk, dv, "masked_attn_tiled")
+        _masked_cache_check(kcache, vcache, nkv, dk * maps, dv, "masked_attn_tiled")
         _i32(page_table, "page_table")
     else:
         _need(vcache is not None and kcache.is_contiguous() and vcache.is_contiguous() and kcache.dtype == vcache.dtype and
-              kcache.shape == (T, nkv * dk) and vcache.shape == (T, nkv * dv), "masked_attn_tiled: the step's own keys and values")
+              kcache.shape == (T, nkv * dk * maps) and vcache.shape == (T, nkv * dv), "masked_attn_tiled: the step's own keys and values")
     _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh), "masked_attn_tiled: sink")
-    _need(n_splits == 1 or (part is not None and part.dtype == torch.float32 and part.is_contiguous() and part.numel() >= T * nh * n_splits * (2 + dv)),
+    _need(n_splits == 1 or (part is not None and part.dtype == torch.float32 and part.is_contiguous() and part.numel() >= T * nh * maps * n_splits * (2 + dv)),
           "masked_attn_tiled: room for the splits' partial results")
     for t, n in ((tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"), (tile_ntok, "tile_ntok"), (tile_pos0, "tile_pos0")):
         _i32(t, n)
@@ -752,7 +775,7 @@ def masked_attn_tiled(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, t
                                           page_table.stride(0) if page_table is not None else 0, kcache.shape[0] if page_table is not None else 0,
                                           _p(tile_seq), _p(tile_tok0), _p(tile_ntok), _p(tile_pos0), int(n_tiles),
                                           int(max_tile_tokens), nh, nkv, dk, dv, ctypes.c_float(scale), int(mask), int(mask_size or 0), _p(sink),
-                                          int(n_splits), _p(part), T, _stream()), launches=2 if n_splits > 1 else 1)
+                                          int(n_splits), _p(part), T, int(maps), _stream()), launches=2 if n_splits > 1 else 1)
 
 
 # ----------------------------------------------------------------------------- gated delta rule
@@ -863,3 +886,65 @@ def moe_combine(x, y, wts, pair_row):
     T, top = wts.shape
     _need(x.shape[0] == T and y.shape[1] == x.shape[1] and pair_row.numel() == T * top, "moe_combine: shapes")
     _check(lib().edgelm_moe_combine(_p(x), _p(y), y.stride(0), _p(wts), _p(pair_row), T, top, x.shape[1], _stream()))
+
+
+# ----------------------------------------------------------------------------- several residual streams
+def streams_fill(x, xs):
+    """xs[t, s] = x[t] for every stream s.  x [T, D], xs [T, S, D], float32."""
+    _f32(x, "x"); _f32(xs, "xs")
+    T, S, D = xs.shape
+    _need(x.shape == (T, D), "streams_fill: shapes")
+    _check(lib().edgelm_streams_fill(_p(x), _p(xs), T, S, D, _stream()))
+
+
+def streams_update(xs, y=None, mix=None, w_out=None, w_in=None, norm_w=None, eps=0.0, h=None):
+    """A residual stream kept as S copies xs [T, S, D] (float32).  With `y` [T, D]: every stream is rewritten from the old
+    ones, xs'[t] = sum_s mix[s, t] xs[s] + w_out[t] y.  With `w_in` [S]: u = sum_s w_in[s] xs'[s] is read out, into `h` as
+    float32, or with `norm_w` [D] as u / sqrt(mean(u^2) + eps) * norm_w in h's type.  Both at once: one pass over xs."""
+    _f32(xs, "xs")
+    T, S, D = xs.shape
+    if y is not None:
+        _f32(y, "y"); _f32(mix, "mix"); _f32(w_out, "w_out")
+        _need(y.shape == (T, D) and mix.shape == (S, S) and w_out.numel() == S, "streams_update: the write's shapes")
+    if w_in is not None:
+        _f32(w_in, "w_in")
+        _need(w_in.numel() == S and h is not None and h.is_contiguous() and h.shape == (T, D), "streams_update: the read's shapes")
+        _need(norm_w is None or (norm_w.dtype == torch.float32 and norm_w.is_contiguous() and norm_w.numel() == D), "streams_update: norm weight")
+    _check(lib().edgelm_streams_update(_p(xs), _p(y), _p(mix), _p(w_out), _p(w_in), _p(norm_w), ctypes.c_float(eps), _p(h),
+                                       _dt(h) if h is not None else 0, T, S, D, _stream()))
+
+
+# ----------------------------------------------------------------------------- real-gated linear recurrent unit
+def rglru_scan(gates, br, bi, u, c, y, by, state, out, seq_tok0, seq_slot, n_seqs, single):
+    """S_t = a S_(t-1) + sqrt(1 - a^2) i u with a = exp(c r), r = sigmoid(gates[:, :W] + br), i = sigmoid(gates[:, W:] + bi);
+    out = S_t gelu_tanh(y + by).  gates [T, 2 W], u [T, W] and y (a view of W columns) float32 rows; c, br, bi, by [W];
+    state [slots, W] float32, read and moved on; `single`: every sequence of the step brings one token."""
+    for t, n in ((gates, "gates"), (br, "br"), (bi, "bi"), (c, "c"), (by, "by"), (state, "state")):
+        _f32(t, n)
+    T, W = out.shape
+    _need(u.dtype == y.dtype == torch.float32 and u.stride(1) == 1 and y.stride(1) == 1 and out.is_contiguous(), "rglru_scan: layout")
+    _need(gates.shape == (T, 2 * W) and u.shape == (T, W) and y.shape == (T, W) and state.shape[1] == W and
+          br.numel() == bi.numel() == c.numel() == by.numel() == W, "rglru_scan: shapes")
+    _i32(seq_tok0, "seq_tok0"); _i32(seq_slot, "seq_slot")
+    _check(lib().edgelm_rglru_scan(_p(gates), gates.stride(0), _p(br), _p(bi), _p(u), u.stride(0), _p(c), _p(y), y.stride(0), _p(by), _p(state),
+                                   _p(out), _dt(out), _p(seq_tok0), _p(seq_slot), int(n_seqs), T, W, 1 if single else 0, _stream()))
+
+
+def clamped_glu(gu, mid, limit, alpha):
+    """mid = g sigmoid(alpha g) (v + 1) with g = min(gate, limit), v = clamp(up, -limit, limit); gu [T, 2 F] float32 = gate | up."""
+    _f32(gu, "gu")
+    T, F = mid.shape
+    _need(gu.shape == (T, 2 * F) and mid.is_contiguous(), "clamped_glu: shapes")
+    _check(lib().edgelm_clamped_glu(_p(gu), _p(mid), _dt(mid), T, F, ctypes.c_float(limit), ctypes.c_float(alpha), _stream()))
+
+
+def diff_combine(a, out, lam, eps, post, w=None):
+    """Two attention maps of a head into one: a [T, H, 2, dv] float32; o = a_1 - lam a_2, divided by its root mean square over
+    dv (`eps` inside the root), times `post` (and `w` [dv], if given); out [T, H dv]."""
+    _f32(a, "a")
+    T = a.shape[0]
+    dv = a.shape[-1]
+    _need(a.dim() == 4 and a.shape[2] == 2 and out.is_contiguous() and out.shape == (T, a.shape[1] * dv), "diff_combine: shapes")
+    _need(w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == dv), "diff_combine: weight")
+    _check(lib().edgelm_diff_combine(_p(a), _p(out), _dt(out), ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(post), _p(w),
+                                     T * a.shape[1], dv, _stream()))

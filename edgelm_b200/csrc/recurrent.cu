@@ -56,11 +56,13 @@ __global__ void save_last_rows_kernel(const TIn* __restrict__ in, float* __restr
 // ------------------------------------------------------------------ short causal convolution + silu
 // Channel c of token t: silu(b[c] + sum_j w[c][j] * in[t - (taps - 1) + j][c]); inputs before the step come from
 // the state [slot][taps - 1][C] (oldest first; zeros before a sequence's start).  `u` holds the inputs at column
-// `off + c` of rows of `ldu` floats.
+// `off + c` of rows of `ldu` floats.  `in_bias` (optional): added to every input that `u` brings, before the
+// convolution (a projection's bias; the state keeps inputs with it, and the zeros before a sequence's start stay zeros).
+// `b` may be null (no bias on the result); `act` 0: no activation.
 __global__ void conv_silu_kernel(const float* __restrict__ u, int ldu, int off, const float* __restrict__ w,
                                  const float* __restrict__ b, const float* __restrict__ state, float* __restrict__ out,
                                  const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_tok0,
-                                 const int32_t* __restrict__ seq_slot, int C, int taps) {
+                                 const int32_t* __restrict__ seq_slot, int C, int taps, const float* __restrict__ in_bias, int act) {
   pdl_launch_dependents();
   pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int t = blockIdx.x;
@@ -69,30 +71,34 @@ __global__ void conv_silu_kernel(const float* __restrict__ u, int ldu, int off, 
   const int k = t - t0;
   const float* st = state + (size_t)seq_slot[s] * (taps - 1) * C;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {   // (few tokens: several blocks a token)
-    float acc = b[c];
+    float acc = b ? b[c] : 0.f;
+    const float ib = in_bias ? in_bias[c] : 0.f;
     for (int j = 0; j < taps; ++j) {
       const int r = k - (taps - 1) + j;
-      const float v = r >= 0 ? u[(size_t)(t0 + r) * ldu + off + c] : st[(size_t)(taps - 1 + r) * C + c];
+      const float v = r >= 0 ? u[(size_t)(t0 + r) * ldu + off + c] + ib : st[(size_t)(taps - 1 + r) * C + c];
       acc = fmaf(w[(size_t)c * taps + j], v, acc);
     }
-    out[(size_t)t * C + c] = silu_exact(acc);
+    out[(size_t)t * C + c] = act ? silu_exact(acc) : acc;
   }
 }
 
 // The state after the step: the last taps - 1 inputs of each sequence.  A thread owns a channel and walks the
 // rows upwards, so that a row it still has to read (one further on) is never overwritten before.
 __global__ void conv_state_update_kernel(const float* __restrict__ u, int ldu, int off, float* __restrict__ state,
-                                         const int32_t* __restrict__ seq_tok0, const int32_t* __restrict__ seq_slot, int C, int taps) {
+                                         const int32_t* __restrict__ seq_tok0, const int32_t* __restrict__ seq_slot, int C, int taps,
+                                         const float* __restrict__ in_bias) {
   pdl_launch_dependents();
   pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int s = blockIdx.x;
   const int t0 = seq_tok0[s], n = seq_tok0[s + 1] - t0;
   float* st = state + (size_t)seq_slot[s] * (taps - 1) * C;
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x)
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    const float ib = in_bias ? in_bias[c] : 0.f;
     for (int j = 0; j < taps - 1; ++j) {
       const int r = n - (taps - 1) + j;
-      st[(size_t)j * C + c] = r >= 0 ? u[(size_t)(t0 + r) * ldu + off + c] : st[(size_t)(j + n) * C + c];
+      st[(size_t)j * C + c] = r >= 0 ? u[(size_t)(t0 + r) * ldu + off + c] + ib : st[(size_t)(j + n) * C + c];
     }
+  }
 }
 
 // Sums over the warp of U values a lane at once: at each of the first log2(U) steps a lane keeps one half of its values
@@ -499,19 +505,25 @@ extern "C" int edgelm_save_last_rows(const void* in, int in_dtype, float* state,
 }
 
 // The convolution over the step's tokens and, with `update_state`, the state for the next step after it (a second launch).
-extern "C" int edgelm_conv_silu(const float* u, int ldu, int off, const float* w, const float* b, float* state, float* out,
-                                const int32_t* tok_seq, const int32_t* seq_tok0, const int32_t* seq_slot, int n_tokens, int n_seqs,
-                                int C, int taps, int update_state, cudaStream_t stream) {
+extern "C" int edgelm_conv_act(const float* u, int ldu, int off, const float* w, const float* b, float* state, float* out,
+                               const int32_t* tok_seq, const int32_t* seq_tok0, const int32_t* seq_slot, int n_tokens, int n_seqs,
+                               int C, int taps, int update_state, const float* in_bias, int act, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && n_seqs > 0 && C > 0 && taps >= 1 && off >= 0 && off + C <= ldu, "conv_silu: bad sizes C=%d taps=%d", C, taps);
   const int col_blocks = n_tokens >= 256 ? 1 : (C + 4 * row_threads(C) - 1) / (4 * row_threads(C));   // a step of few tokens: a block per 4 channels a thread
-  launch_pdl(pdl_bit_for_tokens(n_tokens), conv_silu_kernel, dim3(n_tokens, col_blocks), dim3(row_threads(C)), (size_t)(0), stream, u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, C, taps);
+  launch_pdl(pdl_bit_for_tokens(n_tokens), conv_silu_kernel, dim3(n_tokens, col_blocks), dim3(row_threads(C)), (size_t)(0), stream, u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, C, taps, in_bias, act);
   EL_LAUNCH_CHECK("conv_silu");
   if (taps > 1 && update_state) {
-    launch_pdl(pdl_bit_for_tokens(n_tokens), conv_state_update_kernel, dim3(dim3(n_seqs, (C + 255) / 256)), dim3(256), (size_t)(0), stream, u, ldu, off, state, seq_tok0, seq_slot, C, taps);
+    launch_pdl(pdl_bit_for_tokens(n_tokens), conv_state_update_kernel, dim3(dim3(n_seqs, (C + 255) / 256)), dim3(256), (size_t)(0), stream, u, ldu, off, state, seq_tok0, seq_slot, C, taps, in_bias);
     EL_LAUNCH_CHECK("conv_state_update");
   }
   return 0;
+}
+
+extern "C" int edgelm_conv_silu(const float* u, int ldu, int off, const float* w, const float* b, float* state, float* out,
+                                const int32_t* tok_seq, const int32_t* seq_tok0, const int32_t* seq_slot, int n_tokens, int n_seqs,
+                                int C, int taps, int update_state, cudaStream_t stream) {
+  return edgelm_conv_act(u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, n_tokens, n_seqs, C, taps, update_state, nullptr, 1, stream);
 }
 
 // `conv_state` (may be null): the tail [slot][taps - 1][C] of the convolution whose inputs lie at u[:, conv_off + c];

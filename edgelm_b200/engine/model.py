@@ -28,6 +28,12 @@ class DecoderModel:
         self.head = env.build("head", plan.head)
         self.schedule = plan.schedule
         self.device = None
+        self.streams = int(plan.residual_streams)
+        self._ones = None
+        # arrangements that carry several copies of the residual stream (they answer `first_read`) take xs [tokens, streams, hidden]
+        self.carry = any(hasattr(l, "first_read") for l in self.layers)
+        if self.carry != all(hasattr(l, "first_read") for l in self.layers) or (self.streams > 1 and not self.carry):
+            raise ConfigError(f"a plan with {self.streams} residual streams needs layer arrangements that all carry them")
         for i, e in enumerate(self.schedule):
             need = self.layers[e.layer].cache_need()
             if e.reads_cache_of is not None and need is not None and not getattr(self.layers[e.layer].mixer, "reads_foreign_cache", False):
@@ -60,6 +66,7 @@ class DecoderModel:
             self.head.load(tensors, "", device, tied_table=self.embedding.table)
         else:
             self.head.load(tensors, "", device)
+        self._ones = torch.ones(self.streams, dtype=torch.float32, device=device)
         return self
 
     # ------------------------------------------------------------------ cache and workspace
@@ -79,6 +86,8 @@ class DecoderModel:
     def workspace_bytes(self, n_tokens, n_seqs, n_want):
         d = self.plan.hidden_size
         x = nbytes((n_tokens, d), torch.float32)
+        if self.carry:
+            x += nbytes((n_tokens, self.streams, d), torch.float32) + nbytes((n_tokens, d), self.dtype)
         layers = max(l.workspace_bytes(n_tokens, n_seqs) for l in self.layers)
         head = nbytes((n_want, d), self.dtype)
         return x + max(layers, head) + 4096
@@ -137,11 +146,23 @@ class DecoderModel:
         x = ws.alloc((T, self.plan.hidden_size), torch.float32)
         with ctx.prof("embedding"):
             self.embedding.forward(ctx, x)
+        carried = x
+        if self.carry:
+            # the layers carry `streams` copies of x; each layer's last write also does the read that follows it (the next
+            # layer's first, into `h_next`; after the last layer the sum of the streams, into x)
+            from ..csrc import ops
+            carried = ws.alloc((T, self.streams, self.plan.hidden_size), torch.float32)
+            h_next = ws.alloc((T, self.plan.hidden_size), self.dtype)
+            with ctx.prof("streams"):
+                ops.streams_fill(x, carried)
+            ctx.streams_h = None
         for i, e in enumerate(self.schedule):
             entry = cache.entries[e.reads_cache_of if e.reads_cache_of is not None else i]
             nxt = self.schedule[i + 1].layer if i + 1 < len(self.schedule) else None
             ctx.weights_after = self.layers[nxt].first_weights() if nxt is not None else ()
-            self.layers[e.layer].forward(ctx, x, entry)
+            if self.carry:
+                ctx.streams_next = (*self.layers[nxt].first_read(), h_next, True) if nxt is not None else (self._ones, None, 0.0, x, False)
+            self.layers[e.layer].forward(ctx, carried, entry)
         ctx.weights_after = ()
         if R:
             with ws.frame():

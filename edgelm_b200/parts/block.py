@@ -1,6 +1,7 @@
 """Arrangements of one layer's parts.  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x))
 (adarsh-sgh/edgelm tools/elm.py:122-153); a layer may have no feed-forward.  "sublayer_norm": x += norm1(mixer(x)); x += norm2(ffn(x)), with an
-optional blend of the mixer's input with the previous token's."""
+optional blend of the mixer's input with the previous token's.  "hyper": the pre-norm arrangement over several copies of the
+residual stream, which every sublayer reads through learned weights and rewrites through a learned matrix."""
 import torch
 
 from ..config.base import ConfigError
@@ -186,3 +187,122 @@ class SublayerNormBlock(Part):
                     self.ffn.forward(ctx, h if feeds else x, y, accumulate=False)
                 with ctx.prof("norm_residual"):
                     self.ffn_norm.add_normed(ctx, x, y)
+
+
+@register_block("hyper")
+class HyperBlock(Part):
+    """Pre-norm sublayers over S copies x_1 .. x_S of the residual stream (xs [tokens, S, hidden] float32, all equal at
+    the model's start).  For sublayer q (the mixer, then the feed-forward) with its tensors `in` [S], `out` [S] and `mix`
+    [S, S] (indexed [from, to]):
+
+        u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] y     (all t at once, from the old x)
+
+    One kernel does a write and the read that follows it, also the next layer's (or the sum of the streams after the last
+    layer): `ctx.streams_next` names that read, `ctx.streams_h` says that this layer's first read is done already.
+    Mixers and feed-forwards STORE their output (`accumulate=False`)."""
+
+    def __init__(self, layer_spec, env):
+        self.prefix = layer_spec.prefix
+        self.dtype = env.dtype
+        self.mixer_norm = env.build("norm", layer_spec.mixer_norm)
+        self.mixer = env.build("mixer", layer_spec.mixer)
+        self.ffn_norm = env.build("norm", layer_spec.ffn_norm) if layer_spec.ffn is not None else None
+        self.ffn = env.build("ffn", layer_spec.ffn) if layer_spec.ffn is not None else None
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not getattr(n, "fusable", False):
+                raise ConfigError(f"block 'hyper': the norm '{n.kind}' is not one that the streams' read-out computes (weight, eps)")
+        self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
+        self.hidden = layer_spec.mixer_norm["dim"]
+        self.streams = int(layer_spec.options["streams"])
+        self.names = dict(layer_spec.options["names"])
+        if not 1 <= self.streams <= 8:
+            raise ConfigError(f"block 'hyper': {self.streams} residual streams are not taken (1 to 8)")
+        self.hc = {}
+
+    def _hc_names(self, q):
+        n = self.names
+        return {k: self.prefix + n[q] + n[k] for k in ("in", "out", "mix")}
+
+    def weight_shapes(self, prefix=None):
+        out, S = {}, self.streams
+        for p in self.parts:
+            out.update(p.weight_shapes(self.prefix))
+        for q in ("mixer", "ffn") if self.ffn is not None else ("mixer",):
+            names = self._hc_names(q)
+            out.update({names["in"]: (S,), names["out"]: (S,), names["mix"]: (S, S)})
+        return out
+
+    def load(self, tensors, prefix, device):
+        for p in self.parts:
+            p.load(tensors, self.prefix, device)
+        for q in ("mixer", "ffn") if self.ffn is not None else ("mixer",):
+            self.hc[q] = {k: tensors[name].to(device=device, dtype=torch.float32).contiguous() for k, name in self._hc_names(q).items()}
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def sizes(self):
+        out = {"residual_streams": self.streams}
+        for p in (self.mixer, self.ffn, self.mixer_norm):
+            if p is not None:
+                out.update(p.sizes())
+        return out
+
+    def flops(self, n_tokens, attended):
+        return sum(p.flops(n_tokens, attended) for p in self.parts)
+
+    def describe(self):
+        ffn = f"; {self.ffn_norm.describe()} -> {self.ffn.describe()}" if self.ffn is not None else ""
+        return f"{self.kind} over {self.streams} streams: {self.mixer_norm.describe()} -> {self.mixer.describe()}{ffn}"
+
+    def tile_sizes(self):
+        return tuple(self.mixer.tile_sizes())
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts)
+
+    def workspace_bytes(self, n_tokens, n_seqs):
+        inner = max(self.mixer.workspace_bytes(n_tokens, n_seqs), self.ffn.workspace_bytes(n_tokens, n_seqs) if self.ffn is not None else 0)
+        return nbytes((n_tokens, self.hidden), self.dtype) + nbytes((n_tokens, self.hidden), torch.float32) + inner
+
+    def first_weights(self):
+        return self.mixer.first_weights()
+
+    def first_read(self):
+        """(in-weights, norm weight, eps) of the read that this layer starts with: the layer before may do it with its last write."""
+        return self.hc["mixer"]["in"], self.mixer_norm.weight, self.mixer_norm.eps
+
+    def forward(self, ctx, xs, cache):
+        T, ws = xs.shape[0], ctx.ws
+        after_layer = ctx.weights_after
+        nxt, ctx.streams_next = getattr(ctx, "streams_next", None), None
+        with ws.frame():
+            y = ws.alloc((T, self.hidden), torch.float32)      # a sublayer's output
+            h = getattr(ctx, "streams_h", None)                # this layer's first read, if the layer before did it
+            ctx.streams_h = None
+            if h is None:
+                h = ws.alloc((T, self.hidden), self.dtype)
+                w_in, nw, eps = self.first_read()
+                with ctx.prof("streams"):
+                    ops.streams_update(xs, w_in=w_in, norm_w=nw, eps=eps, h=h)
+            ctx.weights_after = self.ffn.first_weights() if self.ffn is not None else after_layer
+            with ws.frame():
+                self.mixer.forward(ctx, h, y, cache, accumulate=False)
+            ctx.weights_after = after_layer
+            last = self.hc["mixer"]
+            if self.ffn is not None:
+                h2 = ws.alloc((T, self.hidden), self.dtype)
+                with ctx.prof("streams"):
+                    ops.streams_update(xs, y, last["mix"], last["out"], w_in=self.hc["ffn"]["in"], norm_w=self.ffn_norm.weight,
+                                       eps=self.ffn_norm.eps, h=h2)
+                with ws.frame():
+                    self.ffn.forward(ctx, h2, y, accumulate=False)
+                last = self.hc["ffn"]
+            with ctx.prof("streams"):
+                if nxt is not None:
+                    w_in, nw, eps, h_next, is_input = nxt
+                    ops.streams_update(xs, y, last["mix"], last["out"], w_in=w_in, norm_w=nw, eps=eps, h=h_next)
+                    ctx.streams_h = h_next if is_input else None
+                else:
+                    ops.streams_update(xs, y, last["mix"], last["out"])

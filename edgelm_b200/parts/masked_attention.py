@@ -13,13 +13,24 @@ stretched (`parts.rope.rotary_frequencies`).  score = (q . k) * scale.  The mask
 With `sink` (a tensor's name) the softmax's denominator has one more term exp(sink_h) per query head, which has no key
 and no value and is not scaled.  A value head may have another size than a key head.  Angles, scores, the softmax and
 the weighted values are float32 in both precisions; keys and values are kept in the compute dtype.
+
+Options, each with its constants in the spec:
+    conv      a short causal convolution over time on every channel of q, k and v right after the projection (taps
+              [channels, conv], last column the current token's, no bias, zeros before a sequence's start); the last
+              conv - 1 projected rows of a sequence are part of its state
+    qk_norm   {eps}: every query and key head (every map of it) is divided by its root mean square and multiplied by a
+              weight of head_dim values that all heads share (`q_norm`, `k_norm`), before the rotation
+    diff      {offset, eps}: "differential" attention.  A head has two maps, each with queries and keys of head_dim of its
+              own (q and k rows laid out head by head as [map 1, map 2]) and a softmax of its own over the same values.
+              With lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + offset (four tensors of head_dim, one number per layer):
+              o = a_1 - lambda a_2, divided by its root mean square over the head's values (eps), times (1 - offset)
 """
 import torch
 
 from ..config.base import ConfigError
 from ..csrc import ops
 from . import linear
-from .base import KVNeed, Part, as_matrix, as_vector, nbytes
+from .base import KVNeed, NeedSet, Part, StateNeed, as_matrix, as_vector, nbytes
 from .registry import register_mixer
 from .rope import rotary_frequencies
 
@@ -90,18 +101,26 @@ class MaskedAttention(Part):
         self.interleaved = spec.get("rot_pairs", "half") == "interleaved"
         self.rot_base, self.rot_scaling = float(spec.get("rot_base") or 10000.0), spec.get("rot_scaling")
         self.bias = bool(spec.get("bias", False))
+        self.out_bias = bool(spec.get("output_bias", self.bias))
+        self.taps = int(spec.get("conv") or 0)                    # 0: no convolution
+        self.qk_norm, self.diff = spec.get("qk_norm"), spec.get("diff")
+        self.maps = 2 if self.diff else 1
         self.names = dict(spec["names"])
         self.dtype = env.dtype
         if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
             raise ConfigError(f"masked_attention: {self.nh} query heads are not a multiple of {self.nkv} key/value heads")
-        if not (1 <= self.dk <= 1024 and 1 <= self.dv <= 512):
-            raise ConfigError(f"masked_attention: head sizes {self.dk} / {self.dv} are not taken (keys to 1024, values to 512)")
+        if not (1 <= self.dk * self.maps <= 1024 and 1 <= self.dv <= 512):
+            raise ConfigError(f"masked_attention: head sizes {self.dk} / {self.dv} are not taken (key rows to 1024, values to 512)")
+        if self.diff and "sink" in self.names:
+            raise ConfigError("masked_attention: differential maps take no sink")
         if self.rot % 2 or not 0 <= self.rot <= self.dk:
             raise ConfigError(f"masked_attention: {self.rot} rotated dimensions of a head of {self.dk}")
         self.mask, self.mask_size = read_mask(spec.get("mask"), "masked_attention")
-        self.d_qkv = (self.nh + self.nkv) * self.dk + self.nkv * self.dv
+        self.kw = self.dk * self.maps                                # what a head's queries and a key row hold
+        self.d_qkv = (self.nh + self.nkv) * self.kw + self.nkv * self.dv
         self.tile_tokens = max(1, 32 // (self.nh // self.nkv))
-        self.freq = self.b_qkv = self.b_o = self.sink = None
+        self.freq = self.b_qkv = self.b_o = self.sink = self.conv_w = self.q_norm = self.k_norm = self.no_tail = None
+        self.lam = 0.0
 
     def tile_sizes(self):
         return (self.tile_tokens,)
@@ -109,23 +128,37 @@ class MaskedAttention(Part):
     def sizes(self):
         out = {"heads": self.nh, "kv_heads": self.nkv, "head_dim": self.dk, "v_head_dim": self.dv, "rot_dims": self.rot,
                "mask": {v: k for k, v in MASKS.items()}[self.mask], "mask_size": self.mask_size, "sink": "sink" in self.names}
+        if self.taps:
+            out["conv_taps"] = self.taps
+        if self.diff:
+            out["diff_offset"] = float(self.diff["offset"])
+        if self.qk_norm:
+            out["qk_norm"] = True
         return out
 
     def flops(self, n_tokens, attended):
         proj = 2.0 * n_tokens * self.hidden * (self.d_qkv + self.nh * self.dv)
         if self.mask != ops.MASK_CAUSAL:
             attended = min(attended, n_tokens * self.mask_size)
-        return proj + 2.0 * attended * self.nh * (self.dk + self.dv)
+        return proj + 2.0 * attended * self.nh * self.maps * (self.dk + self.dv)
 
     def weight_shapes(self, prefix):
         n = self.names
-        out = {prefix + n["q"]: (self.nh * self.dk, self.hidden), prefix + n["k"]: (self.nkv * self.dk, self.hidden),
-               prefix + n["v"]: (self.nkv * self.dv, self.hidden), prefix + n["o"]: (self.hidden, self.nh * self.dv)}
+        rows = {"q": self.nh * self.kw, "k": self.nkv * self.kw, "v": self.nkv * self.dv}
+        out = {prefix + n[k]: (r, self.hidden) for k, r in rows.items()}
+        out[prefix + n["o"]] = (self.hidden, self.nh * self.dv)
         if self.bias:
-            out.update({prefix + n["q"] + n["bias"]: (self.nh * self.dk,), prefix + n["k"] + n["bias"]: (self.nkv * self.dk,),
-                        prefix + n["v"] + n["bias"]: (self.nkv * self.dv,), prefix + n["o"] + n["bias"]: (self.hidden,)})
+            out.update({prefix + n[k] + n["bias"]: (r,) for k, r in rows.items()})
+        if self.out_bias:
+            out[prefix + n["o"] + n["bias"]] = (self.hidden,)
         if "sink" in n:
             out[prefix + n["sink"]] = (self.nh,)
+        if self.taps:
+            out.update({prefix + n[k] + n["conv"]: (r, self.taps) for k, r in rows.items()})
+        if self.qk_norm:
+            out.update({prefix + n["q_norm"]: (self.dk,), prefix + n["k_norm"]: (self.dk,)})
+        if self.diff:
+            out.update({prefix + n[k]: (self.dk,) for k in ("lq1", "lk1", "lq2", "lk2")})
         return out
 
     def load(self, tensors, prefix, device):
@@ -134,7 +167,16 @@ class MaskedAttention(Part):
         self.w_o = as_matrix(tensors[prefix + n["o"]], self.dtype, device)
         if self.bias:
             self.b_qkv = torch.cat([as_vector(tensors[prefix + n[k] + n["bias"]], device) for k in ("q", "k", "v")]).contiguous()
+        if self.out_bias:
             self.b_o = as_vector(tensors[prefix + n["o"] + n["bias"]], device)
+        if self.taps:
+            self.conv_w = torch.cat([as_matrix(tensors[prefix + n[k] + n["conv"]], torch.float32, device) for k in ("q", "k", "v")], dim=0).contiguous()
+            self.no_tail = torch.zeros((1, 0, self.d_qkv), dtype=torch.float32, device=device)      # (one tap: no earlier row is kept)
+        if self.qk_norm:
+            self.q_norm, self.k_norm = as_vector(tensors[prefix + n["q_norm"]], device), as_vector(tensors[prefix + n["k_norm"]], device)
+        if self.diff:
+            l = {k: tensors[prefix + n[k]].to(torch.float64) for k in ("lq1", "lk1", "lq2", "lk2")}
+            self.lam = float(torch.exp((l["lq1"] * l["lk1"]).sum()) - torch.exp((l["lq2"] * l["lk2"]).sum())) + float(self.diff["offset"])
         if "sink" in n:
             self.sink = as_vector(tensors[prefix + n["sink"]], device)
         if self.rot:
@@ -146,12 +188,17 @@ class MaskedAttention(Part):
     def cache_need(self):
         # (a window's pages could be given back as the sequence moves on, `KVNeed.window`; the kernels here read through
         # the whole table, so every page is kept)
-        return KVNeed(self.nkv, self.dk, None, v_head_dim=self.dv)
+        kv = KVNeed(self.nkv, self.kw, None, v_head_dim=self.dv)
+        if self.taps > 1:
+            return NeedSet.of(kv=kv, conv=StateNeed((self.taps - 1, self.d_qkv)))
+        return kv
 
     def workspace_bytes(self, n_tokens, n_seqs):
-        return (nbytes((n_tokens, self.d_qkv), torch.float32) + nbytes((n_tokens, self.nh * self.dk), torch.float32) +
-                nbytes((n_tokens, self.nh * self.dv), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype) +
-                splits_room(n_seqs, self.nh, self.dv))
+        f32 = torch.float32
+        return (nbytes((n_tokens, self.d_qkv), f32) * (2 if self.taps else 1) + nbytes((n_tokens, self.nh * self.kw), f32) +
+                nbytes((n_tokens, self.nh * self.maps * self.dv), f32 if self.diff else self.dtype) +
+                (nbytes((n_tokens, self.nh * self.dv), self.dtype) if self.diff else 0) + nbytes((n_tokens, self.hidden), self.dtype) +
+                splits_room(n_seqs, self.nh * self.maps, self.dv))
 
     def forward(self, ctx, h, x, cache, accumulate=True):
         h = linear.as_tensor(h)
@@ -159,26 +206,42 @@ class MaskedAttention(Part):
         qkv = ws.alloc((T, self.d_qkv), torch.float32)
         with ctx.prof("qkv_proj"):
             linear.matmul(ctx, h, self.w_qkv, qkv, prefetch=(self.w_o,))
-        q = ws.alloc((T, self.nh * self.dk), torch.float32)
+        bias = self.b_qkv
+        if self.taps:
+            conv = cache.get("conv") if self.taps > 1 else None
+            cache = cache["kv"] if self.taps > 1 else cache
+            mixed = ws.alloc((T, self.d_qkv), torch.float32)
+            with ctx.prof("qkv_conv"):
+                ops.conv_act(qkv, 0, self.conv_w, None, conv.state if conv is not None else self.no_tail, mixed, ctx.tok_seq, ctx.seq_tok0,
+                             ctx.seq_slots, ctx.n_seqs, update_state=True, in_bias=bias, act=None)
+            qkv, bias = mixed, None
+        q = ws.alloc((T, self.nh * self.kw), torch.float32)
         table = ctx.page_table(cache.group)
         with ctx.prof("rotate_append"):
-            ops.rotate_append(qkv, self.b_qkv, q, ctx.tok_pos, ctx.tok_seq, table, cache.k, cache.v, self.nh, self.nkv, self.dk, self.dv,
-                              self.rot, self.interleaved, self.freq, ctx.err)
-        a = ws.alloc((T, self.nh * self.dv), self.dtype)
+            ops.rotate_append(qkv, bias, q, ctx.tok_pos, ctx.tok_seq, table, cache.k, cache.v, self.nh, self.nkv, self.kw, self.dv,
+                              self.rot, self.interleaved, self.freq, ctx.err, maps=self.maps, q_norm=self.q_norm, k_norm=self.k_norm,
+                              eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
+        a = ws.alloc((T, self.nh * self.maps * self.dv), torch.float32 if self.diff else self.dtype)
         with ctx.prof("attn_masked"):
             if ctx.all_single and self.nh // self.nkv >= SHARED_KEYS_MIN_GROUP:
-                splits = decode_splits(ctx, self.nkv, self.nh // self.nkv, self.mask, self.mask_size)
-                part = ws.alloc((T * self.nh * splits * (2 + self.dv),), torch.float32) if splits > 1 else None
+                splits = decode_splits(ctx, self.nkv * self.maps, self.nh // self.nkv, self.mask, self.mask_size)
+                part = ws.alloc((T * self.nh * self.maps * splits * (2 + self.dv),), torch.float32) if splits > 1 else None
                 tseq, ttok0, tntok, tpos0 = single_token_tiles(ctx)
                 ops.masked_attn_tiled(q, a, cache.k, cache.v, table, tseq, ttok0, tntok, tpos0, T, 1, self.nh, self.nkv, self.dk, self.dv,
-                                      self.scale, self.mask, self.mask_size, self.sink, n_splits=splits, part=part)
+                                      self.scale, self.mask, self.mask_size, self.sink, n_splits=splits, part=part, maps=self.maps)
             elif ctx.all_single:
                 ops.masked_attn(q, a, cache.k, cache.v, ctx.tok_pos, ctx.tok_seq, table, self.nh, self.nkv, self.dk, self.dv, self.scale,
-                                self.mask, self.mask_size, self.sink, most_keys(self.mask, self.mask_size))
+                                self.mask, self.mask_size, self.sink, most_keys(self.mask, self.mask_size), maps=self.maps)
             else:
                 tiles = ctx.tiles(self.tile_tokens)
                 ops.masked_attn_tiled(q, a, cache.k, cache.v, table, tiles.seq, tiles.tok0, tiles.ntok, tiles.pos0, tiles.count,
-                                      self.tile_tokens, self.nh, self.nkv, self.dk, self.dv, self.scale, self.mask, self.mask_size, self.sink)
+                                      self.tile_tokens, self.nh, self.nkv, self.dk, self.dv, self.scale, self.mask, self.mask_size, self.sink,
+                                      maps=self.maps)
+        if self.diff:
+            o = ws.alloc((T, self.nh * self.dv), self.dtype)
+            with ctx.prof("diff_combine"):
+                ops.diff_combine(a.view(T, self.nh, 2, self.dv), o, self.lam, float(self.diff["eps"]), 1.0 - float(self.diff["offset"]))
+            a = o
         with ctx.prof("o_proj"):
             linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL if accumulate else linear.EPI_STORE,
                           residual=x if accumulate else None, prefetch=ctx.weights_after)
