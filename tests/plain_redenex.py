@@ -3,7 +3,9 @@ first token: no cache, no state, no batches.  What the library computes is compa
 
 A model is (config, weights): `config` is the config.json dictionary, `weights` maps tensor names to arrays.
 """
+import json
 import math
+import os
 
 import numpy as np
 
@@ -51,9 +53,10 @@ def rotate_half_pairs(x, positions, dims, base):
 
 def rglru_mixer(h, w, m, pre):
     """The recurrent block: a gelu branch and a convolved branch that feeds a gated diagonal recurrence."""
-    W, blocks = m["width"], m["blocks"]
+    W, blocks = m["width"], m.get("blocks", 1)
     y = gelu_tanh(h @ w[pre + "y"].T + w[pre + "y.b"])
-    u = causal_conv(h @ w[pre + "x"].T + w[pre + "x.b"], w[pre + "conv"], w[pre + "conv.b"])
+    u = h @ w[pre + "x"].T + w[pre + "x.b"]
+    u = causal_conv(u, w[pre + "conv"], w[pre + "conv.b"])
     bw = W // blocks
     ub = u.reshape(-1, blocks, bw)
     r = sigmoid(np.einsum("bok,nbk->nbo", w[pre + "ra"], ub) + w[pre + "ra.b"]).reshape(-1, W)
@@ -69,14 +72,43 @@ def rglru_mixer(h, w, m, pre):
     return (out * y) @ w[pre + "o"].T
 
 
+def chunked_softmax_attention(q, k, v, scale, chunk=None):
+    """q [n, H, d], k [n, G, d], v [n, G, e] from position 0: position i sees the j <= i of its own chunk (all j <= i without
+    one); query head h reads key/value head h // (H / G).  -> [n, H, e]"""
+    n, H = q.shape[0], q.shape[1]
+    G = k.shape[1]
+    pos = np.arange(n)
+    seen = pos[None, :] <= pos[:, None]
+    if chunk:
+        seen &= (pos[None, :] // chunk) == (pos[:, None] // chunk)
+    out = np.zeros((n, H, v.shape[2]))
+    for head in range(H):
+        g = head // (H // G)
+        s = np.where(seen, (q[:, head] @ k[:, g].T) * scale, -np.inf)
+        p = np.exp(s - s.max(axis=1, keepdims=True))
+        out[:, head] = (p / p.sum(axis=1, keepdims=True)) @ v[:, g]
+    return out
+
+
+def map_weight(w, pre, offset):
+    """lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + offset: one number per layer."""
+    return math.exp(float(np.sum(w[pre + "lq1"] * w[pre + "lk1"]))) - math.exp(float(np.sum(w[pre + "lq2"] * w[pre + "lk2"]))) + offset
+
+
+def combine_maps(a1, a2, lam, offset, eps):
+    """o = a1 - lambda a2, divided by its root mean square over a head's values, times (1 - offset)."""
+    return rms_norm(a1 - lam * a2, eps) * (1.0 - offset)
+
+
 def differential_attention(h, w, m, pre, eps):
     """Two softmax maps per head over the same values, subtracted, normed per head."""
     n = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     pos = np.arange(n)
-    q = causal_conv(h @ w[pre + "q"].T + w[pre + "q.b"], w[pre + "q.conv"]).reshape(n, H, 2, d)
-    k = causal_conv(h @ w[pre + "k"].T + w[pre + "k.b"], w[pre + "k.conv"]).reshape(n, G, 2, d)
-    v = causal_conv(h @ w[pre + "v"].T + w[pre + "v.b"], w[pre + "v.conv"]).reshape(n, G, dv)
+    q, k, v = (h @ w[pre + s].T + w[pre + s + ".b"] for s in "qkv")
+    if m.get("conv"):
+        q, k, v = (causal_conv(t, w[pre + s + ".conv"]) for t, s in zip((q, k, v), "qkv"))
+    q, k, v = q.reshape(n, H, 2, d), k.reshape(n, G, 2, d), v.reshape(n, G, dv)
     q = rms_norm(q, eps, w[pre + "q.norm"])
     k = rms_norm(k, eps, w[pre + "k.norm"])
     rot = m.get("rot")
@@ -84,23 +116,9 @@ def differential_attention(h, w, m, pre, eps):
         q = rotate_half_pairs(q, pos, rot["dims"], rot["base"])
         k = rotate_half_pairs(k, pos, rot["dims"], rot["base"])
     size = (m.get("mask") or {}).get("size")
-    seen = pos[None, :] <= pos[:, None]
-    if size:
-        seen &= (pos[None, :] // size) == (pos[:, None] // size)
-    lam = math.exp(float(np.sum(w[pre + "lq1"] * w[pre + "lk1"]))) - math.exp(float(np.sum(w[pre + "lq2"] * w[pre + "lk2"]))) + m["diff"]
-    out = np.zeros((n, H, dv))
-    for head in range(H):
-        g = head // (H // G)
-        maps = []
-        for j in range(2):
-            s = (q[:, head, j] @ k[:, g, j].T) * m["scale"]
-            s = np.where(seen, s, -np.inf)
-            p = np.exp(s - s.max(axis=1, keepdims=True))
-            p /= p.sum(axis=1, keepdims=True)
-            maps.append(p @ v[:, g])
-        o = maps[0] - lam * maps[1]
-        out[:, head] = rms_norm(o, eps) * (1.0 - m["diff"])
-    return out.reshape(n, H * dv) @ w[pre + "o"].T
+    a1, a2 = (chunked_softmax_attention(q[:, :, j], k[:, :, j], v, m["scale"], size) for j in range(2))
+    o = combine_maps(a1, a2, map_weight(w, pre, m["diff"]), m["diff"], eps)
+    return o.reshape(n, H * dv) @ w[pre + "o"].T
 
 
 def clamped_glu(h, w, mlp, pre):
@@ -159,3 +177,33 @@ def forward(config, weights, tokens, return_layers=False):
         x = xs.sum(axis=0)
     logits = rms_norm(x, eps, w["final.norm"], True) @ w["head"].T
     return (logits, np.stack(after)) if return_layers else logits
+
+
+def read_safetensors(path):
+    """name -> float64 array, from the file format itself (8-byte length, JSON header, data); bfloat16, float32 and int32."""
+    with open(path, "rb") as f:
+        n = int.from_bytes(f.read(8), "little")
+        header = json.loads(f.read(n))
+        data = f.read()
+    out = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = info["data_offsets"]
+        raw = data[a:b]
+        if info["dtype"] == "BF16":
+            arr = (np.frombuffer(raw, dtype="<u2").astype(np.uint32) << 16).view(np.float32)
+        elif info["dtype"] == "F32":
+            arr = np.frombuffer(raw, dtype="<f4")
+        elif info["dtype"] == "I32":
+            arr = np.frombuffer(raw, dtype="<i4")
+        else:
+            raise ValueError(info["dtype"])
+        out[name] = arr.astype(np.float64).reshape(info["shape"])
+    return out
+
+
+def load(model_dir):
+    with open(os.path.join(model_dir, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, read_safetensors(os.path.join(model_dir, "model.safetensors"))
