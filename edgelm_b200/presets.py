@@ -39,7 +39,25 @@ def _vosulorn(vocab, width, ff, groups_of_layers, heads, kv_heads, kv_rank, rot_
             "max_positions": 8192, "layers": [delta, latent, delta, attn] * groups_of_layers}
 
 
+def _redenex(vocab, width, ff, pattern, rec_width, rec_blocks, heads, kv_heads, dim, chunk, streams):
+    """A Redenex-shaped model: recurrent ("r") and attention ("a") layers in the order of `pattern`, each with a clamped
+    gated feed-forward; an attention head has two maps of `dim` and values of 2 * dim (so heads * 2 * dim query rows, as many
+    as a plain decoder of the same width has), the recurrent mixer is `rec_width` wide in `rec_blocks` blocks; `streams` copies
+    of the residual stream."""
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    rec = {"type": "rglru", "mlp": dense, "mixer": {"width": rec_width, "blocks": rec_blocks, "conv": 4}}
+    att = {"type": "attention", "mlp": dense, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": 2 * dim, "conv": 3, "diff": 0.8, "scale": dim ** -0.5,
+        "mask": {"size": chunk}, "rot": {"base": 500000.0, "dims": dim}}}
+    return {"architecture": "Redenex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "streams": streams, "max_positions": 8192, "layers": [rec if c == "r" else att for c in pattern]}
+
+
 PRESETS = {
+    # the layer sizes of smollm2-135m and smollm2-1.7b (width, feed-forward, as many query, key and output rows, vocabulary)
+    # in the Redenex design: two recurrent layers to one of attention, four residual streams
+    "redenex-576": _redenex(49152, 576, 1536, "rrarrarr", 768, 12, 9, 3, 32, 1024, 4),
+    "redenex-2048": _redenex(49152, 2048, 8192, "rrar", 2560, 16, 16, 16, 64, 1024, 4),
     # the layer sizes of smollm2-135m and smollm2-1.7b (width, heads of 64, vocabulary; a token's two experts together as
     # wide as the dense feed-forward) in the Vosulorn design
     "vosulorn-576": _vosulorn(49152, 576, 768, 2, 9, 3, 128, 32, 1024, 8, 2),
