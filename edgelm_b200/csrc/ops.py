@@ -915,10 +915,19 @@ def streams_update(xs, y=None, mix=None, w_out=None, w_in=None, norm_w=None, eps
 
 
 # ----------------------------------------------------------------------------- real-gated linear recurrent unit
-def rglru_scan(gates, br, bi, u, c, y, by, state, out, seq_tok0, seq_slot, n_seqs, single):
+RGLRU_SEG = 64        # tokens of a prompt step that one block of the scan composes (RG_SEG in rglru.cu)
+
+
+def rglru_scratch_floats(n_tokens, n_seqs, W):
+    """Floats of scratch that a prompt step of the scan needs: a starting state per sequence and a map per segment."""
+    return (n_seqs + 2 * ((n_tokens + RGLRU_SEG - 1) // RGLRU_SEG)) * W
+
+
+def rglru_scan(gates, br, bi, u, c, y, by, state, out, seq_tok0, seq_slot, n_seqs, single, tok_seq=None, scratch=None):
     """S_t = a S_(t-1) + sqrt(1 - a^2) i u with a = exp(c r), r = sigmoid(gates[:, :W] + br), i = sigmoid(gates[:, W:] + bi);
     out = S_t gelu_tanh(y + by).  gates [T, 2 W], u [T, W] and y (a view of W columns) float32 rows; c, br, bi, by [W];
-    state [slots, W] float32, read and moved on; `single`: every sequence of the step brings one token."""
+    state [slots, W] float32, read and moved on; `single`: every sequence of the step brings one token.  Other steps name
+    every token's sequence (`tok_seq` [T] int32) and bring `scratch`, float32 of `rglru_scratch_floats` elements."""
     for t, n in ((gates, "gates"), (br, "br"), (bi, "bi"), (c, "c"), (by, "by"), (state, "state")):
         _f32(t, n)
     T, W = out.shape
@@ -926,8 +935,13 @@ def rglru_scan(gates, br, bi, u, c, y, by, state, out, seq_tok0, seq_slot, n_seq
     _need(gates.shape == (T, 2 * W) and u.shape == (T, W) and y.shape == (T, W) and state.shape[1] == W and
           br.numel() == bi.numel() == c.numel() == by.numel() == W, "rglru_scan: shapes")
     _i32(seq_tok0, "seq_tok0"); _i32(seq_slot, "seq_slot")
+    if not single:
+        _i32(tok_seq, "tok_seq"); _f32(scratch, "scratch")
+        _need(tok_seq.numel() >= T and scratch.numel() >= rglru_scratch_floats(T, int(n_seqs), W), "rglru_scan: tok_seq and scratch sizes")
     _check(lib().edgelm_rglru_scan(_p(gates), gates.stride(0), _p(br), _p(bi), _p(u), u.stride(0), _p(c), _p(y), y.stride(0), _p(by), _p(state),
-                                   _p(out), _dt(out), _p(seq_tok0), _p(seq_slot), int(n_seqs), T, W, 1 if single else 0, _stream()))
+                                   _p(out), _dt(out), _p(seq_tok0), _p(seq_slot), _p(tok_seq) if not single else None,
+                                   _p(scratch) if not single else None, int(n_seqs), T, W, 1 if single else 0, _stream()),
+           launches=1 if single else 2)
 
 
 def clamped_glu(gu, mid, limit, alpha):

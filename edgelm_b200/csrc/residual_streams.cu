@@ -26,56 +26,99 @@ __global__ void streams_fill_kernel(const float* __restrict__ x, float* __restri
   }
 }
 
-template <typename TO>
+// V floats at once (V 4 when rows are 16-byte aligned, else 1); SM: the unrolled loops' bound on the streams (S <= SM)
+template <int V> struct RsVec { float e[V]; };
+template <int V> __device__ __forceinline__ RsVec<V> rs_load(const float* p) {
+  RsVec<V> r;
+  if constexpr (V == 4) { const float4 q = *reinterpret_cast<const float4*>(p); r.e[0] = q.x; r.e[1] = q.y; r.e[2] = q.z; r.e[3] = q.w; }
+  else r.e[0] = *p;
+  return r;
+}
+template <int V> __device__ __forceinline__ void rs_store(float* p, const RsVec<V>& r) {
+  if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(r.e[0], r.e[1], r.e[2], r.e[3]);
+  else *p = r.e[0];
+}
+template <int V> __device__ __forceinline__ void rs_store(__nv_bfloat16* p, const RsVec<V>& r) {
+  if constexpr (V == 4) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(r.e[0], r.e[1]), hi = __floats2bfloat162_rn(r.e[2], r.e[3]);
+    uint2 q;
+    q.x = *reinterpret_cast<const unsigned*>(&lo);
+    q.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = q;
+  } else *p = __float2bfloat16(r.e[0]);
+}
+
+template <typename TO, int V, int SM>
 __global__ void __launch_bounds__(RS_THREADS)
 streams_update_kernel(float* __restrict__ xs, const float* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ w_out,
                       const float* __restrict__ w_in, const float* __restrict__ norm_w, float eps, TO* __restrict__ h, int S, int D) {
   pdl_launch_dependents();
-  extern __shared__ float rs_u[];        // D floats: the read-out of this token, kept between the two passes
+  extern __shared__ __align__(16) float rs_u[];        // D floats: the read-out of this token, kept between the two passes
   __shared__ float red[33];
-  __shared__ float cm[RS_MAX * RS_MAX], co[RS_MAX], ci[RS_MAX];
-  if (threadIdx.x < S * S && y) cm[threadIdx.x] = mix[threadIdx.x];
-  if (threadIdx.x < S) {
-    co[threadIdx.x] = y ? w_out[threadIdx.x] : 0.f;
-    ci[threadIdx.x] = w_in ? w_in[threadIdx.x] : 0.f;
+  __shared__ float cm[SM * SM], co[SM], ci[SM];
+  // (weights past S are zero: the unrolled sums run to SM)
+  if (threadIdx.x < SM * SM) {
+    const int f = threadIdx.x / SM, t = threadIdx.x % SM;
+    cm[threadIdx.x] = (y && f < S && t < S) ? mix[f * S + t] : 0.f;
+  }
+  if (threadIdx.x < SM) {
+    co[threadIdx.x] = (y && threadIdx.x < S) ? w_out[threadIdx.x] : 0.f;
+    ci[threadIdx.x] = (w_in && threadIdx.x < S) ? w_in[threadIdx.x] : 0.f;
   }
   pdl_wait();
   __syncthreads();
   float* row = xs + (size_t)blockIdx.x * S * D;
   const float* yr = y ? y + (size_t)blockIdx.x * D : nullptr;
   float ss = 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float v[RS_MAX];
+  for (int d = threadIdx.x * V; d < D; d += blockDim.x * V) {
+    RsVec<V> v[SM];
 #pragma unroll
-    for (int s = 0; s < RS_MAX; ++s) v[s] = s < S ? row[(size_t)s * D + d] : 0.f;
+    for (int s = 0; s < SM; ++s) {
+      if (s < S) v[s] = rs_load<V>(row + (size_t)s * D + d);
+      else
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[s].e[e] = 0.f;
+    }
     if (yr) {
-      const float yv = yr[d];
-      float n[RS_MAX];
+      const RsVec<V> yv = rs_load<V>(yr + d);
+      RsVec<V> n[SM];
 #pragma unroll
-      for (int t = 0; t < RS_MAX; ++t) {
-        float a = 0.f;
+      for (int t = 0; t < SM; ++t)
 #pragma unroll
-        for (int s = 0; s < RS_MAX; ++s)
-          if (s < S && t < S) a = fmaf(cm[s * S + t], v[s], a);
-        n[t] = fmaf(co[t < S ? t : 0], yv, a);
-      }
+        for (int e = 0; e < V; ++e) {
+          float a = 0.f;
 #pragma unroll
-      for (int t = 0; t < RS_MAX; ++t)
-        if (t < S) { v[t] = n[t]; row[(size_t)t * D + d] = n[t]; }
+          for (int s = 0; s < SM; ++s) a = fmaf(cm[s * SM + t], v[s].e[e], a);
+          n[t].e[e] = fmaf(co[t], yv.e[e], a);
+        }
+#pragma unroll
+      for (int t = 0; t < SM; ++t)
+        if (t < S) { v[t] = n[t]; rs_store<V>(row + (size_t)t * D + d, n[t]); }
     }
     if (w_in) {
-      float u = 0.f;
+      RsVec<V> u;
 #pragma unroll
-      for (int s = 0; s < RS_MAX; ++s)
-        if (s < S) u = fmaf(ci[s], v[s], u);
-      if (norm_w) { rs_u[d] = u; ss = fmaf(u, u, ss); }
-      else h[(size_t)blockIdx.x * D + d] = from_f32<TO>(u);
+      for (int e = 0; e < V; ++e) {
+        float a = 0.f;
+#pragma unroll
+        for (int s = 0; s < SM; ++s) a = fmaf(ci[s], v[s].e[e], a);
+        u.e[e] = a;
+        ss = fmaf(a, a, ss);
+      }
+      if (norm_w) rs_store<V>(rs_u + d, u);
+      else rs_store<V>(h + (size_t)blockIdx.x * D + d, u);
     }
   }
   if (!w_in || !norm_w) return;
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) h[(size_t)blockIdx.x * D + d] = from_f32<TO>(rs_u[d] * inv * norm_w[d]);
+  for (int d = threadIdx.x * V; d < D; d += blockDim.x * V) {
+    RsVec<V> u = rs_load<V>(rs_u + d);
+    const RsVec<V> w = rs_load<V>(norm_w + d);
+#pragma unroll
+    for (int e = 0; e < V; ++e) u.e[e] = u.e[e] * inv * w.e[e];
+    rs_store<V>(h + (size_t)blockIdx.x * D + d, u);
+  }
 }
 
 }  // namespace edgelm
@@ -102,17 +145,19 @@ extern "C" int edgelm_streams_update(float* xs, const float* y, const float* mix
   const size_t smem = (w_in && norm_w) ? (size_t)D * sizeof(float) : 0;
   EL_REFUSE(smem <= 200 * 1024, "streams_update: rows of %d values are not taken", D);
   const int bit = pdl_bit_for_tokens(n_tokens);
-  if (h_dtype == DT_BF16) {
-    auto kern = streams_update_kernel<__nv_bfloat16>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_pdl(bit, kern, dim3(n_tokens), dim3(RS_THREADS), smem, stream, xs, y, mix, w_out, w_in, norm_w, eps, (__nv_bfloat16*)h, S, D);
-  } else if (h_dtype == DT_F32) {
-    auto kern = streams_update_kernel<float>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_pdl(bit, kern, dim3(n_tokens), dim3(RS_THREADS), smem, stream, xs, y, mix, w_out, w_in, norm_w, eps, (float*)h, S, D);
-  } else {
-    EL_REFUSE(false, "streams_update: unknown dtype code %d", h_dtype);
-  }
+  EL_REFUSE(h == nullptr || h_dtype == DT_BF16 || h_dtype == DT_F32, "streams_update: unknown dtype code %d", h_dtype);
+  // four values at once where every row starts on 16 bytes (8 for a bfloat16 read-out)
+  const bool vec = D % 4 == 0 && (uintptr_t)xs % 16 == 0 && (y == nullptr || (uintptr_t)y % 16 == 0) && (norm_w == nullptr || (uintptr_t)norm_w % 16 == 0) &&
+                   (h == nullptr || (uintptr_t)h % 16 == 0);
+  const int sm = S <= 2 ? 2 : S <= 4 ? 4 : 8;
+#define EL_RS(TO, V, SM) do { auto kern = streams_update_kernel<TO, V, SM>; \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    launch_pdl(bit, kern, dim3(n_tokens), dim3(RS_THREADS), smem, stream, xs, y, mix, w_out, w_in, norm_w, eps, (TO*)h, S, D); } while (0)
+#define EL_RS_V(TO, V) do { if (sm == 2) EL_RS(TO, V, 2); else if (sm == 4) EL_RS(TO, V, 4); else EL_RS(TO, V, 8); } while (0)
+  if (h_dtype == DT_BF16) { if (vec) EL_RS_V(__nv_bfloat16, 4); else EL_RS_V(__nv_bfloat16, 1); }
+  else { if (vec) EL_RS_V(float, 4); else EL_RS_V(float, 1); }
+#undef EL_RS_V
+#undef EL_RS
   EL_LAUNCH_CHECK("streams_update");
   return 0;
 }

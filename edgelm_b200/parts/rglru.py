@@ -74,6 +74,7 @@ class RGLRU(Part):
     def workspace_bytes(self, n_tokens, n_seqs):
         f32, W = torch.float32, self.width
         return (nbytes((n_tokens, 2 * W), f32) * 2 + nbytes((n_tokens, W), f32) + nbytes((n_tokens, W), self.dtype) +
+                nbytes((ops.rglru_scratch_floats(n_tokens, n_seqs, W),), f32) +
                 nbytes((n_tokens, self.hidden), self.dtype))
 
     def forward(self, ctx, h, x, cache, accumulate=True):
@@ -93,8 +94,9 @@ class RGLRU(Part):
             ops.head_matmul(u, self.bw, self.w_ri, gates[:, W:], self.bw)
         s = ws.alloc((T, W), self.dtype)
         with ctx.prof("rglru_scan"):
+            scratch = None if ctx.all_single else ws.alloc((ops.rglru_scratch_floats(T, ctx.n_seqs, W),), f32)
             ops.rglru_scan(gates, self.b_ra, self.b_ri, u, self.decay, yx[:, :W], self.b_y, cache["rglru"].state, s,
-                           ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs, ctx.all_single)
+                           ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs, ctx.all_single, tok_seq=ctx.tok_seq, scratch=scratch)
         with ctx.prof("rglru_out_proj"):
             linear.matmul(ctx, s, self.w_o, x, epilogue=linear.EPI_RESIDUAL if accumulate else linear.EPI_STORE,
                           residual=x if accumulate else None, prefetch=ctx.weights_after)

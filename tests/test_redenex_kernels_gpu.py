@@ -22,9 +22,10 @@ DEV = "cuda:0"
 def test_recurrent_unit_over_steps(W, blocks, taps, out_dtype):
     """Convolution with both biases, block-wise gates, decay and recurrence, fed in pieces (down to one token, shorter than
     the convolution's tail) on state rows in no particular order; a slot of nobody is never touched.  Decays close to 1:
-    what a state held forty tokens ago still shows."""
+    what a state held forty tokens ago still shows.  The last step packs the end of one sequence and the start of the next
+    into one segment of the scan and runs over several segments."""
     g = np.random.default_rng(W + taps)
-    total, cuts, slots = [43, 6, 1, 70], [[5, 1, 37], [2, 4], [1], [1, 1, 68]], [4, 0, 2, 5]
+    total, cuts, slots = [43, 6, 1, 270], [[5, 1, 37], [2, 4], [1], [1, 1, 268]], [4, 0, 2, 5]
     bw = W // blocks
     w = {"y": np.eye(W), "y.b": g.uniform(-0.5, 0.5, W), "x": np.eye(W), "x.b": g.uniform(-0.5, 0.5, W), "conv": g.normal(0, 0.6, size=(W, taps)),
          "conv.b": g.uniform(-0.3, 0.3, W), "ra": g.normal(0, 1.5 / np.sqrt(bw), size=(blocks, bw, bw)), "ra.b": g.uniform(-1, 1, (blocks, bw)),
@@ -56,7 +57,8 @@ def test_recurrent_unit_over_steps(W, blocks, taps, out_dtype):
         ops.head_matmul(u, bw, f32(w["ri"]), gates[:, W:], bw)
         o = torch.full((T, W), float("nan"), dtype=out_dtype, device=DEV)
         ops.rglru_scan(gates, f32(w["ra.b"].reshape(-1)), f32(w["ri.b"].reshape(-1)), u, decay, yx[:, :W], f32(w["y.b"]), state, o, tok0, seqslot,
-                       len(live), all(n == 1 for _, _, n in live))
+                       len(live), all(n == 1 for _, _, n in live), tok_seq=tok_seq,
+                       scratch=torch.full((ops.rglru_scratch_floats(T, len(live), W),), float("nan"), device=DEV))
         o = o.float().cpu().numpy()
         at = 0
         for s, a, n in live:
