@@ -39,6 +39,9 @@ struct RopeAppend {
   __nv_bfloat16* kcache;
   __nv_bfloat16* vcache;
   int table_stride, n_pages, max_pos, nh, nkv, hd;
+  // the gated epilogue's form (the struct travels to every kernel, so its constants ride along): out = g sigmoid(alpha g) v with
+  // g = min(gate, limit), v = clamp(up, -limit, limit) + shift; limit 0: no clamps (alpha 1, shift 0: SwiGLU)
+  float glu_limit = 0.f, glu_alpha = 1.f, glu_shift = 0.f;
 };
 
 // Grouped products (a feed-forward of experts): the rows of `a` come grouped, every group's rows starting at a multiple of
@@ -53,14 +56,19 @@ constexpr int TC_BM = 128;   // rows of `a` per tile = lanes of tensor memory
 constexpr int TC_STAGES = 3;   // ring stages of the one-tile kernel when several blocks share an SM (48 KB stages: 144 KB)
 constexpr int TC_DEEP_BYTES = 192 * 1024;   // ring of the one-tile kernel when the grid is at most one block an SM
 constexpr int TC_THREADS = 192;
+// The gated unit of the epilogue: silu(gate) * up, or its clamped form with a slope inside the sigmoid and a shifted up branch.
 // z / (1 + e^-z) with the exponential and the reciprocal on the special-function unit (2^x and 1/x to about 2^-22):
 // the result is rounded to bfloat16 right after; an epilogue thread computes 64 to 128 of these while its tile's
 // tensor memory is held.  (z < -88: 2^x overflows to infinity, the reciprocal is 0 and the result -0, the limit.)
-__device__ __forceinline__ float silu_tc(float z) {
+__device__ __forceinline__ float glu_tc(float g, float v, float limit, float alpha, float shift) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    v = fminf(fmaxf(v, -limit), limit);
+  }
   float e, r;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * alpha * -1.4426950408889634f));
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-  return z * r;
+  return g * r * (v + shift);
 }
 
 template <typename TOut> struct OutVec;
@@ -106,7 +114,7 @@ __device__ __forceinline__ void fetch_residual(ResidualAhead& ra, const float* r
 template <int EPI, typename TOut>
 __device__ __forceinline__ void epilogue_piece(const uint32_t* r, const uint32_t* r2, TOut* out, int ldo,
                                                const float* residual, int row, int col0, int M, int N, int vec_ok,
-                                               const ResidualAhead* ahead = nullptr) {
+                                               const RopeAppend& form, const ResidualAhead* ahead = nullptr) {
   if (row >= M) return;
   const size_t base = (size_t)row * ldo + col0;
   const bool full = vec_ok && (col0 + 32 <= N);
@@ -116,7 +124,7 @@ __device__ __forceinline__ void epilogue_piece(const uint32_t* r, const uint32_t
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float acc = __uint_as_float(r[j0 + j]);
-      if (EPI == TC_EPI_SWIGLU) v[j] = silu_tc(acc) * __uint_as_float(r2[j0 + j]);
+      if (EPI == TC_EPI_SWIGLU) v[j] = glu_tc(acc, __uint_as_float(r2[j0 + j]), form.glu_limit, form.glu_alpha, form.glu_shift);
       else v[j] = acc;
     }
     if (full) {
@@ -403,7 +411,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           continue;
         }
-        epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok, &ra[(c0 >> 5) & 1]);
+        epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok, rope, &ra[(c0 >> 5) & 1]);
       }
     }
   }
@@ -418,7 +426,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // out = epilogue(sum over the splits, in their order, of the raw sums a split-K launch left).
 template <int EPI, typename TOut>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, TOut* out, int ldo, const float* residual,
-                                     int M, int N) {
+                                     int M, int N, float glu_limit, float glu_alpha, float glu_shift) {
   constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
   const size_t plane = (size_t)M * N;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < plane; i += (size_t)gridDim.x * blockDim.x) {
@@ -429,7 +437,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     }
     const int m = (int)(i / N), n = (int)(i - (size_t)m * N);
     const size_t o = (size_t)m * ldo + n;
-    if (EPI == TC_EPI_SWIGLU) out[o] = from_f32<TOut>(silu_tc(a) * b);
+    if (EPI == TC_EPI_SWIGLU) out[o] = from_f32<TOut>(glu_tc(a, b, glu_limit, glu_alpha, glu_shift));
     else if (EPI == TC_EPI_RESIDUAL) out[o] = from_f32<TOut>(residual[o] + a);
     else out[o] = from_f32<TOut>(a);
   }
@@ -571,7 +579,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           tmem_ld32(acc_addr + (uint32_t)c0, r);
           if (NB == 2) tmem_ld32(acc_addr + (uint32_t)c0 + BN, r2);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok);
+          epilogue_piece<EPI, TOut>(r, r2, out, ldo, residual, m0 + q * 32 + lane, n0 + c0, M, N, vec_ok, rope);
         }
       }
       // this warp's rows of the stage are in registers or stored: hand the stage back to the MMA warp
@@ -690,7 +698,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   if (EPI != TC_EPI_ROPE && splits > 1) {
     const size_t plane = (size_t)M * N;
     const int blocks = (int)((plane + 255) / 256 < 1184 ? (plane + 255) / 256 : 1184);
-    splitk_reduce_kernel<EPI, TOut><<<blocks, 256, 0, stream>>>(g_splitk_ws, splits, (TOut*)out, ldo, residual, M, N);
+    splitk_reduce_kernel<EPI, TOut><<<blocks, 256, 0, stream>>>(g_splitk_ws, splits, (TOut*)out, ldo, residual, M, N, rope.glu_limit, rope.glu_alpha, rope.glu_shift);
   }
   return 0;
 }
@@ -825,6 +833,17 @@ static int gemm_tc_run(const void* a, int lda, const void* w, const void* w2, vo
   if (rc) return rc;
   EL_LAUNCH_CHECK("gemm_tc");
   return 0;
+}
+
+// out = g sigmoid(alpha g) (v + shift) with g = min(a w^T, limit), v = clamp(a w2^T, -limit, limit): the gated epilogue in its clamped form
+extern "C" int edgelm_gemm_tc_glu(const void* a, int lda, const void* w, const void* w2, void* out, int ldo, int M, int N, int K,
+                                  int out_dtype, float limit, float alpha, float shift, int* err, cudaStream_t stream) {
+  EL_REFUSE(limit > 0.f && w2 != nullptr, "gemm_tc_glu: needs a positive limit and the second weight");
+  RopeAppend form{};
+  form.glu_limit = limit;
+  form.glu_alpha = alpha;
+  form.glu_shift = shift;
+  return gemm_tc_run(a, lda, w, w2, out, ldo, nullptr, M, N, K, out_dtype, TC_EPI_SWIGLU, err, stream, form);
 }
 
 extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void* w2, void* out, int ldo,

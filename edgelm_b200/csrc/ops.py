@@ -225,8 +225,9 @@ def _splitk_ready():
         lib().edgelm_gemm_tc_splitk(_p(_splitk_scratch), SPLITK_SCRATCH_BYTES, 1)
 
 
-def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None):
-    """out = a @ w.T (+ epilogue) on the tcgen05 tensor cores: bfloat16 operands, float32 accumulation."""
+def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None, glu=None):
+    """out = a @ w.T (+ epilogue) on the tcgen05 tensor cores: bfloat16 operands, float32 accumulation.  `glu` (limit, alpha,
+    shift) with the gated epilogue: out = g sigmoid(alpha g) (v + shift), g = min(a @ w.T, limit), v = clamp(a @ w2.T, -limit, limit)."""
     _splitk_ready()
     _need(a.dim() == 2 and w.dim() == 2 and out.dim() == 2, "gemm_tc: 2-D operands")
     M, K = a.shape
@@ -237,8 +238,13 @@ def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None):
     _need(w2 is None or (w2.dtype == w.dtype and w2.shape == w.shape and w2.is_contiguous()), "gemm_tc: second weight")
     if residual is not None:
         _need(residual.dtype == torch.float32 and residual.shape == out.shape and residual.stride() == out.stride(), "gemm_tc: residual layout")
-    _check(lib().edgelm_gemm_tc(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), _p(residual), M, N, K, _dt(out),
-                                epilogue, _p(err), _stream()), launches=0)
+    if glu is not None:
+        _need(epilogue == EPI_SWIGLU and w2 is not None and residual is None and glu[0] > 0, "gemm_tc: the clamped gated epilogue needs both weights and a limit")
+        _check(lib().edgelm_gemm_tc_glu(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), M, N, K, _dt(out), ctypes.c_float(glu[0]),
+                                        ctypes.c_float(glu[1]), ctypes.c_float(glu[2]), _p(err), _stream()), launches=0)
+    else:
+        _check(lib().edgelm_gemm_tc(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), _p(residual), M, N, K, _dt(out),
+                                    epilogue, _p(err), _stream()), launches=0)
     count_launches(lib().edgelm_gemm_tc_last_launches())
 
 
@@ -942,6 +948,22 @@ def rglru_scan(gates, br, bi, u, c, y, by, state, out, seq_tok0, seq_slot, n_seq
                                    _p(out), _dt(out), _p(seq_tok0), _p(seq_slot), _p(tok_seq) if not single else None,
                                    _p(scratch) if not single else None, int(n_seqs), T, W, 1 if single else 0, _stream()),
            launches=1 if single else 2)
+
+
+def rglru_gates(u, w_ra, w_ri, gates, blocks):
+    """gates[:, :W] and gates[:, W:] <- the block-diagonal products of u [T, W] float32 with w_ra and w_ri [blocks, W / blocks,
+    W / blocks] ([out, in] per block), float32 sums.  bfloat16 matrices run on the tensor cores with the input split into three
+    bfloat16 terms (exact products, float32 sums); float32 matrices take the plain float32 kernel, a matrix at a time."""
+    _f32(u, "u"); _f32(gates, "gates")
+    T, W = u.shape
+    bw = W // blocks
+    _need(W % blocks == 0 and gates.shape == (T, 2 * W) and w_ra.shape == w_ri.shape == (blocks, bw, bw) and w_ra.dtype == w_ri.dtype and
+          w_ra.is_contiguous() and w_ri.is_contiguous() and u.stride(1) == 1, "rglru_gates: shapes")
+    if w_ra.dtype == torch.bfloat16:
+        _check(lib().edgelm_rglru_gates(_p(u), u.stride(0), _p(w_ra), _p(w_ri), _p(gates), gates.stride(0), T, W, int(blocks), _stream()))
+    else:
+        head_matmul(u, bw, w_ra, gates[:, :W], bw)
+        head_matmul(u, bw, w_ri, gates[:, W:], bw)
 
 
 def clamped_glu(gu, mid, limit, alpha):

@@ -161,6 +161,99 @@ __global__ void rglru_step_kernel(const float* __restrict__ gates, int ldg, cons
   out[(size_t)t * W + ch] = from_f32<TO>(S * gelu_tanh_f(y[(size_t)t * ldy + ch] + by[ch]));
 }
 
+// The gates' products on the tensor cores, exact to float32: gates[t][b bw + n] = sum_k ra[b][n][k] u[t][b bw + k] and the same
+// with ri into the second half of the row.  The weights are bfloat16; a float32 input is the sum of three bfloat16 terms
+// (8 + 8 + 8 bits of its 24), every product of a term and a weight is exact in float32, and the sums are float32: the
+// result differs from the float32 product by the order of the sums only.  A block takes 64 tokens x 32 columns of both
+// matrices of one diagonal block (they share the staged input), a warp 16 tokens, K in chunks of 32.
+constexpr int GT_M = 64, GT_N = 32, GT_KC = 32, GT_LD = GT_KC + 8;      // (rows of 40 bfloat16: fragment reads hit 32 banks)
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 lo, __nv_bfloat16 hi) {
+  return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+}
+
+__global__ void __launch_bounds__(128)
+rglru_gates_mma_kernel(const float* __restrict__ u, int ldu, const __nv_bfloat16* __restrict__ w_ra, const __nv_bfloat16* __restrict__ w_ri,
+                       float* __restrict__ gates, int ldg, int n_tokens, int W, int bw) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ __align__(16) __nv_bfloat16 As[3][GT_M][GT_LD];
+  __shared__ __align__(16) __nv_bfloat16 Ws[2 * GT_N][GT_LD];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, cq = lane & 3;
+  const int t0 = blockIdx.x * GT_M, n0 = blockIdx.y * GT_N, blk = blockIdx.z;
+  const float* ub = u + (size_t)blk * bw;
+  float acc[8][4] = {};
+  for (int k0 = 0; k0 < bw; k0 += GT_KC) {
+    // the input: pairs of neighbours along K, each value split into three bfloat16 terms
+    for (int i = threadIdx.x; i < GT_M * (GT_KC / 2); i += 128) {
+      const int r = i / (GT_KC / 2), k = (i - r * (GT_KC / 2)) * 2;
+      const bool row = t0 + r < n_tokens;
+      float x[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) x[e] = (row && k0 + k + e < bw) ? ub[(size_t)(t0 + r) * ldu + k0 + k + e] : 0.f;
+      __nv_bfloat16 p[3][2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float rest = x[e];
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+          p[q][e] = __float2bfloat16(rest);
+          rest -= __bfloat162float(p[q][e]);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 3; ++q) *reinterpret_cast<uint32_t*>(&As[q][r][k]) = pack_bf16(p[q][0], p[q][1]);
+    }
+    // the weights: rows n0 .. n0 + 31 of ra[blk], then of ri[blk]
+    for (int i = threadIdx.x; i < 2 * GT_N * GT_KC; i += 128) {
+      const int r = i / GT_KC, k = i - r * GT_KC, n = n0 + (r % GT_N);
+      const __nv_bfloat16* wm = r < GT_N ? w_ra : w_ri;
+      Ws[r][k] = (n < bw && k0 + k < bw) ? wm[((size_t)blk * bw + n) * bw + k0 + k] : __float2bfloat16(0.f);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GT_KC; kk += 16) {
+      uint32_t af[3][4];
+#pragma unroll
+      for (int q = 0; q < 3; ++q) {
+        const __nv_bfloat16* base = &As[q][warp * 16 + gq][kk + cq * 2];
+        af[q][0] = *reinterpret_cast<const uint32_t*>(base);
+        af[q][1] = *reinterpret_cast<const uint32_t*>(base + 8 * GT_LD);
+        af[q][2] = *reinterpret_cast<const uint32_t*>(base + 8);
+        af[q][3] = *reinterpret_cast<const uint32_t*>(base + 8 * GT_LD + 8);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const __nv_bfloat16* wb = &Ws[j * 8 + gq][kk + cq * 2];
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(wb), b1 = *reinterpret_cast<const uint32_t*>(wb + 8);
+        mma_bf16_16816(acc[j], af[2], b0, b1);      // the smallest terms first
+        mma_bf16_16816(acc[j], af[1], b0, b1);
+        mma_bf16_16816(acc[j], af[0], b0, b1);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int n = n0 + (j % 4) * 8 + cq * 2;
+    float* dst = gates + (j < 4 ? 0 : W) + (size_t)blk * bw + n;
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+      const int t = t0 + warp * 16 + gq + hrow * 8;
+      if (t < n_tokens) {
+        if (n < bw) dst[(size_t)t * ldg] = acc[j][hrow * 2];
+        if (n + 1 < bw) dst[(size_t)t * ldg + 1] = acc[j][hrow * 2 + 1];
+      }
+    }
+  }
+}
+
 // mid = g sigmoid(alpha g) (v + 1) with g = min(gate, limit), v = clamp(up, -limit, limit); gu [tokens][2 F] float32 = gate | up
 template <typename TO>
 __global__ void clamped_glu_kernel(const float* __restrict__ gu, TO* __restrict__ mid, int F, float limit, float alpha) {
@@ -204,6 +297,19 @@ extern "C" int edgelm_rglru_scan(const float* gates, int ldg, const float* br, c
     else launch_pdl(bit, rglru_walk_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, gates, ldg, br, bi, u, ldu, c, y, ldy, by, (const float*)seg, (const float*)init, state, (__nv_bfloat16*)out, seq_tok0, seq_slot, tok_seq, n_tokens, W);
   }
   EL_LAUNCH_CHECK("rglru_scan");
+  return 0;
+}
+
+// gates [tokens][>= 2 W] float32 <- the block-diagonal products of u [tokens][W..] float32 with ra and ri [blocks][bw][bw] bfloat16
+extern "C" int edgelm_rglru_gates(const float* u, int ldu, const void* w_ra, const void* w_ri, float* gates, int ldg, int n_tokens, int W,
+                                  int blocks, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && W > 0 && blocks > 0 && W % blocks == 0 && ldu >= W && ldg >= 2 * W && blocks <= 65535, "rglru_gates: bad sizes (width %d, %d blocks)", W, blocks);
+  const int bw = W / blocks;
+  const dim3 grid((n_tokens + GT_M - 1) / GT_M, (bw + GT_N - 1) / GT_N, blocks), block(128);
+  launch_pdl(pdl_bit_for_tokens(n_tokens), rglru_gates_mma_kernel, grid, block, (size_t)0, stream, u, ldu, (const __nv_bfloat16*)w_ra,
+             (const __nv_bfloat16*)w_ri, gates, ldg, n_tokens, W, bw);
+  EL_LAUNCH_CHECK("rglru_gates");
   return 0;
 }
 

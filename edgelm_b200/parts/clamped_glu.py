@@ -1,7 +1,8 @@
 """A gated feed-forward with clamped branches: g = min(h Wg^T, limit), v = clamp(h Wu^T, -limit, limit),
-x += (g * sigmoid(alpha g) * (v + 1)) Wd^T, no bias.  `limit` and `alpha` are constants of the spec.  Gate and up are one
-matrix product over the two weights stacked; its float32 sums feed the activation kernel, whose result (in the compute
-dtype) is the down projection's input; the residual sum is the down projection's epilogue."""
+x += (g * sigmoid(alpha g) * (v + 1)) Wd^T, no bias.  `limit` and `alpha` are constants of the spec.  Prompt steps in
+bfloat16 compute the unit in the epilogue of the tensor-core product of gate and up (two accumulators a tile); other steps
+run one matrix product over the two weights stacked, whose float32 sums feed the activation kernel.  Either way the result
+(in the compute dtype) is the down projection's input, and the residual sum is the down projection's epilogue."""
 import torch
 
 from ..config.base import ConfigError
@@ -50,13 +51,19 @@ class ClampedGLU(Part):
 
     def forward(self, ctx, h, x, accumulate=True):
         """x += feed_forward(h); with `accumulate` False, x = feed_forward(h) (float32)."""
-        T = h.shape[0]
-        gu = ctx.ws.alloc((T, 2 * self.inter), torch.float32)
-        with ctx.prof("gate_up"):
-            linear.matmul(ctx, h, self.w_gu, gu, prefetch=(self.w_down,))
-        mid = ctx.ws.alloc((T, self.inter), self.dtype)
-        with ctx.prof("clamped_glu"):
-            ops.clamped_glu(gu, mid, self.limit, self.alpha)
+        T, F = h.shape[0], self.inter
+        mid = ctx.ws.alloc((T, F), self.dtype)
+        w_gate, w_up = self.w_gu[:F], self.w_gu[F:]
+        if T > linear.FEW_ROWS and self.dtype == torch.bfloat16 and ops.gemm_tc_takes(linear.as_tensor(h), w_gate, mid, w_up):
+            # prompt steps in bfloat16: the gate and up products share a tile and the unit is the product's epilogue
+            with ctx.prof("gate_up_clamped_glu"):
+                ops.gemm_tc(linear.as_tensor(h), w_gate, mid, ctx.err, epilogue=linear.EPI_SWIGLU, w2=w_up, glu=(self.limit, self.alpha, 1.0))
+        else:
+            gu = ctx.ws.alloc((T, 2 * F), torch.float32)
+            with ctx.prof("gate_up"):
+                linear.matmul(ctx, h, self.w_gu, gu, prefetch=(self.w_down,))
+            with ctx.prof("clamped_glu"):
+                ops.clamped_glu(gu, mid, self.limit, self.alpha)
         with ctx.prof("down_proj_residual"):
             linear.matmul(ctx, mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL if accumulate else linear.EPI_STORE,
                           residual=x if accumulate else None, prefetch=ctx.weights_after)

@@ -90,8 +90,7 @@ class RGLRU(Part):
                          ctx.tok_seq, ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs, update_state=True, in_bias=self.b_x, act=None)
         gates = ws.alloc((T, 2 * W), f32)
         with ctx.prof("rglru_gates"):
-            ops.head_matmul(u, self.bw, self.w_ra, gates[:, :W], self.bw)
-            ops.head_matmul(u, self.bw, self.w_ri, gates[:, W:], self.bw)
+            ops.rglru_gates(u, self.w_ra, self.w_ri, gates, self.blocks)
         s = ws.alloc((T, W), self.dtype)
         with ctx.prof("rglru_scan"):
             scratch = None if ctx.all_single else ws.alloc((ops.rglru_scratch_floats(T, ctx.n_seqs, W),), f32)

@@ -53,8 +53,7 @@ def test_recurrent_unit_over_steps(W, blocks, taps, out_dtype):
         u = torch.full((T, W), float("nan"), device=DEV)
         ops.conv_act(yx, W, f32(w["conv"]), f32(w["conv.b"]), tail, u, tok_seq, tok0, seqslot, len(live), update_state=True, in_bias=f32(w["x.b"]), act=None)
         gates = torch.full((T, 2 * W), float("nan"), device=DEV)
-        ops.head_matmul(u, bw, f32(w["ra"]), gates[:, :W], bw)
-        ops.head_matmul(u, bw, f32(w["ri"]), gates[:, W:], bw)
+        ops.rglru_gates(u, f32(w["ra"]), f32(w["ri"]), gates, blocks)
         o = torch.full((T, W), float("nan"), dtype=out_dtype, device=DEV)
         ops.rglru_scan(gates, f32(w["ra.b"].reshape(-1)), f32(w["ri.b"].reshape(-1)), u, decay, yx[:, :W], f32(w["y.b"]), state, o, tok0, seqslot,
                        len(live), all(n == 1 for _, _, n in live), tok_seq=tok_seq,
@@ -68,6 +67,26 @@ def test_recurrent_unit_over_steps(W, blocks, taps, out_dtype):
     for x, o in zip(want, got):
         assert np.abs(o - x).max() < tol * max(1.0, np.abs(x).max())
     assert torch.isnan(state[1]).all()
+
+
+@pytest.mark.parametrize("w_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("W,blocks,T", [(96, 3, 37), (70, 2, 5), (33, 3, 1), (320, 5, 200), (480, 3, 131), (40, 1, 64)])
+def test_gate_products_are_float32(W, blocks, T, w_dtype):
+    """The block-diagonal gate products keep the float32 input's low bits (rounding the input to bfloat16 would miss by a
+    thousand times the tolerance), for block widths that are odd, below a tile and several tiles."""
+    g = np.random.default_rng(W + T)
+    bw = W // blocks
+    u = torch.tensor(g.normal(size=(T, W)) * 3.0, dtype=torch.float32)
+    ws = [torch.tensor(g.normal(0, 1.0, size=(blocks, bw, bw)), dtype=torch.float32).to(torch.bfloat16) for _ in range(2)]
+    want = [np.einsum("bnk,tbk->tbn", w.double().numpy(), u.double().numpy().reshape(T, blocks, bw)).reshape(T, W) for w in ws]
+    gates = torch.full((T, 2 * W), float("nan"), device=DEV)
+    ops.rglru_gates(u.to(DEV), ws[0].to(device=DEV, dtype=w_dtype), ws[1].to(device=DEV, dtype=w_dtype), gates, blocks)
+    got = gates.cpu().double().numpy()
+    scale = 3.0 * np.sqrt(bw)
+    tol = (1e-5 if w_dtype == torch.bfloat16 else 3e-6) * scale       # (the tensor cores' float32 sums drop the bits below the running sum's last one)
+    assert np.abs(got[:, :W] - want[0]).max() < tol and np.abs(got[:, W:] - want[1]).max() < tol
+    lossy = np.einsum("bnk,tbk->tbn", ws[0].double().numpy(), u.to(torch.bfloat16).double().numpy().reshape(T, blocks, bw)).reshape(T, W)
+    assert np.abs(lossy - want[0]).max() > 1e-4 * scale      # (the check above can tell the two apart)
 
 
 # ----------------------------------------------------------------------------- residual streams
@@ -122,6 +141,29 @@ def test_clamped_gated_unit(T, F, limit, alpha, dtype):
     if alpha == 1.702:      # the plain function itself, with identity matrices
         w = {"gate": np.eye(F), "up": np.eye(F), "down": np.eye(F)}
         assert np.allclose(plain.clamped_glu(a[:, :F], {**w, "up": np.zeros((F, F))}, {"limit": limit}, ""), gate * plain.sigmoid(1.702 * gate))
+
+
+@pytest.mark.parametrize("T,D,F,limit,alpha", [(200, 64, 130, 1.5, 1.702), (37, 48, 56, 0.7, 1.0), (300, 192, 1024, 7.0, 1.702)])
+def test_clamped_gated_unit_in_the_product(T, D, F, limit, alpha):
+    """The same unit as the epilogue of the tensor-core product of gate and up (prompt steps in bfloat16), against the plain
+    feed-forward with an identity down projection; both clamps bite."""
+    g = np.random.default_rng(T + F)
+    bf = lambda a: torch.tensor(a, dtype=torch.float32).to(torch.bfloat16)
+    h, wg, wu = bf(g.normal(size=(T, D))), bf(g.normal(0, 2.0 * limit / np.sqrt(D), size=(F, D))), bf(g.normal(0, 2.0 * limit / np.sqrt(D), size=(F, D)))
+    w = {"gate": wg.double().numpy(), "up": wu.double().numpy(), "down": np.eye(F)}
+    a = h.double().numpy()
+    assert (a @ w["gate"].T > limit).any() and (a @ w["up"].T < -limit).any() and (a @ w["up"].T > limit).any()
+    gate, up = np.minimum(a @ w["gate"].T, limit), np.clip(a @ w["up"].T, -limit, limit)
+    want = gate * plain.sigmoid(alpha * gate) * (up + 1.0)
+    if alpha == 1.702:
+        assert np.allclose(want, plain.clamped_glu(a, w, {"limit": limit}, ""))
+    mid = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    w_gu = torch.cat([wg, wu]).to(DEV).contiguous()
+    assert ops.gemm_tc_takes(h.to(DEV), w_gu[:F], mid, w_gu[F:])
+    ops.gemm_tc(h.to(DEV), w_gu[:F], mid, err, epilogue=ops.EPI_SWIGLU, w2=w_gu[F:], glu=(limit, alpha, 1.0))
+    assert int(err.abs().sum()) == 0
+    assert np.abs(mid.float().cpu().numpy() - want).max() < 1e-2 * max(1.0, np.abs(want).max())
 
 
 # ----------------------------------------------------------------------------- norm and rotation per map, into the cache
