@@ -925,15 +925,16 @@ RGLRU_SEG = 64        # tokens of a prompt step that one block of the scan compo
 
 
 def rglru_scratch_floats(n_tokens, n_seqs, W):
-    """Floats of scratch that a prompt step of the scan needs: a starting state per sequence and a map per segment."""
-    return (n_seqs + 2 * ((n_tokens + RGLRU_SEG - 1) // RGLRU_SEG)) * W
+    """Floats of scratch that a prompt step of the scan needs: a map (two rows of W) per segment."""
+    return 2 * ((n_tokens + RGLRU_SEG - 1) // RGLRU_SEG) * W
 
 
 def rglru_scan(gates, br, bi, u, c, y, by, state, out, seq_tok0, seq_slot, n_seqs, single, tok_seq=None, scratch=None):
     """S_t = a S_(t-1) + sqrt(1 - a^2) i u with a = exp(c r), r = sigmoid(gates[:, :W] + br), i = sigmoid(gates[:, W:] + bi);
     out = S_t gelu_tanh(y + by).  gates [T, 2 W], u [T, W] and y (a view of W columns) float32 rows; c, br, bi, by [W];
     state [slots, W] float32, read and moved on; `single`: every sequence of the step brings one token.  Other steps name
-    every token's sequence (`tok_seq` [T] int32) and bring `scratch`, float32 of `rglru_scratch_floats` elements."""
+    every token's sequence (`tok_seq` [T] int32), bring `scratch`, float32 of `rglru_scratch_floats` elements, and leave
+    decays and inputs in `gates`."""
     for t, n in ((gates, "gates"), (br, "br"), (bi, "bi"), (c, "c"), (by, "by"), (state, "state")):
         _f32(t, n)
     T, W = out.shape

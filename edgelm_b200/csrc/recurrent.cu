@@ -510,7 +510,10 @@ extern "C" int edgelm_conv_act(const float* u, int ldu, int off, const float* w,
                                int C, int taps, int update_state, const float* in_bias, int act, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && n_seqs > 0 && C > 0 && taps >= 1 && off >= 0 && off + C <= ldu, "conv_silu: bad sizes C=%d taps=%d", C, taps);
-  const int col_blocks = n_tokens >= 256 ? 1 : (C + 4 * row_threads(C) - 1) / (4 * row_threads(C));   // a step of few tokens: a block per 4 channels a thread
+  // several blocks a token, so that a thread's loads are few and many blocks overlap theirs: 4 channels a thread in steps of
+  // few tokens, 2 in prompt steps (one block a token there left a thread ten channels in a row at a width of 2,560)
+  const int per_thread = n_tokens >= 256 ? 2 : 4;
+  const int col_blocks = (C + per_thread * row_threads(C) - 1) / (per_thread * row_threads(C));
   launch_pdl(pdl_bit_for_tokens(n_tokens), conv_silu_kernel, dim3(n_tokens, col_blocks), dim3(row_threads(C)), (size_t)(0), stream, u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, C, taps, in_bias, act);
   EL_LAUNCH_CHECK("conv_silu");
   if (taps > 1 && update_state) {

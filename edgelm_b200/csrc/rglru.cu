@@ -8,8 +8,8 @@
 // Everything is float32; the state [slot][W] is read at a step's start and written at its end.  A recurrence
 // S_t = a_t S_(t-1) + b_t composes: (a, b) then (a', b') is (a a', a' b + b').  Prompt steps use that in two passes over
 // segments of RG_SEG consecutive tokens of the step (a block owns 32 channels of one segment, a lane a channel, a warp a run of
-// RG_RUN tokens): the first composes every segment into one map, the second folds the maps before a segment in a fixed
-// order and walks the segment from the state that gives.  A sequence's first token of the step is the constant map that
+// RG_RUN tokens): the first turns gates into decays and inputs and composes every segment into one map, the second folds the
+// maps before a segment in a fixed order and walks the segment from the state that gives.  A sequence's first token of the step is the constant map that
 // starts from the state the sequence left, so segments may hold the ends and starts of several sequences.  Steps of one
 // token a sequence use a thread per (sequence, channel).
 #include "common.cuh"
@@ -30,55 +30,49 @@ __device__ __forceinline__ void rglru_terms(float gr, float gi, float u, float c
   *b = sqrtf(-expm1f(2.0f * la)) * sigmoid_f(gi) * u;
 }
 
-// One run of RG_RUN tokens of one channel, from the step's first token `first` on: decay and input of every token.  A
-// sequence's first token of the step takes the state that the sequence left (`from` [seq][W]) instead of its neighbour's:
-// it is the constant map (0, a S_left + b).  `last`: bit j says that token j ends its sequence's part of the step.
-__device__ __forceinline__ void rglru_run(const float* __restrict__ gates, int ldg, const float* __restrict__ u, int ldu, float cc, float cbr,
-                                          float cbi, const float* __restrict__ from, bool from_slots, const int32_t* __restrict__ seq_tok0,
-                                          const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ tok_seq, int first, int n_tokens,
-                                          int W, int ch, bool live, float* a, float* b, unsigned* last, float* keep) {
-  *last = 0;
-#pragma unroll
-  for (int j = 0; j < RG_RUN; ++j) {
-    a[j] = 1.f;
-    b[j] = 0.f;
-    const int t = first + j;
-    if (live && t < n_tokens) {
-      rglru_terms(gates[(size_t)t * ldg + ch] + cbr, gates[(size_t)t * ldg + W + ch] + cbi, u[(size_t)t * ldu + ch], cc, &a[j], &b[j]);
-      const int s = tok_seq[t];
-      if (t == seq_tok0[s]) {
-        const float v = from[(size_t)(from_slots ? seq_slot[s] : s) * W + ch];
-        if (keep) keep[(size_t)s * W + ch] = v;
-        b[j] = fmaf(a[j], v, b[j]);
-        a[j] = 0.f;
-      }
-      if (t + 1 == seq_tok0[s + 1]) *last |= 1u << j;
-    }
-  }
-}
-
-// Prompt steps, first pass: block (channels, segment) composes its RG_SEG tokens into one map (A, B) per channel,
-// seg [segment][2][W], and keeps the states that the step's sequences start from, init [seq][W].
+// Prompt steps, first pass: block (channels, segment) turns the gates of its RG_SEG tokens into decay and input, IN PLACE
+// (gates[t][ch] <- a, gates[t][W + ch] <- b), and composes them into one map (A, B) per channel, seg [segment][2][W].  A
+// sequence's first token of the step takes the state that the sequence left instead of its neighbour's: it becomes the
+// constant map (0, a S_left + b).
 __global__ void __launch_bounds__(RG_WARPS * 32)
-rglru_compose_kernel(const float* __restrict__ gates, int ldg, const float* __restrict__ br, const float* __restrict__ bi,
+rglru_compose_kernel(float* __restrict__ gates, int ldg, const float* __restrict__ br, const float* __restrict__ bi,
                      const float* __restrict__ u, int ldu, const float* __restrict__ c, const float* __restrict__ state,
-                     float* __restrict__ seg, float* __restrict__ init, const int32_t* __restrict__ seq_tok0,
-                     const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ tok_seq, int n_tokens, int W) {
+                     float* __restrict__ seg, const int32_t* __restrict__ seq_tok0, const int32_t* __restrict__ seq_slot,
+                     const int32_t* __restrict__ tok_seq, int n_tokens, int W) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float runA[RG_WARPS][32], runB[RG_WARPS][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ch = blockIdx.x * 32 + lane, g = blockIdx.y;
   const bool live = ch < W;
-  float a[RG_RUN], b[RG_RUN];
-  unsigned last;
-  rglru_run(gates, ldg, u, ldu, live ? c[ch] : 0.f, live ? br[ch] : 0.f, live ? bi[ch] : 0.f, state, true, seq_tok0, seq_slot, tok_seq,
-            g * RG_SEG + warp * RG_RUN, n_tokens, W, ch, live, a, b, &last, init);
+  const int first = g * RG_SEG + warp * RG_RUN;
+  const float cc = live ? c[ch] : 0.f, cbr = live ? br[ch] : 0.f, cbi = live ? bi[ch] : 0.f;
+  float gr[RG_RUN], gi[RG_RUN], uv[RG_RUN];
+#pragma unroll
+  for (int j = 0; j < RG_RUN; ++j) {           // (all loads first: they do not depend on one another)
+    const bool on = live && first + j < n_tokens;
+    const size_t t = (size_t)(first + j);
+    gr[j] = on ? gates[t * ldg + ch] : 0.f;
+    gi[j] = on ? gates[t * ldg + W + ch] : 0.f;
+    uv[j] = on ? u[t * ldu + ch] : 0.f;
+  }
   float A = 1.f, B = 0.f;
 #pragma unroll
   for (int j = 0; j < RG_RUN; ++j) {
-    A *= a[j];
-    B = fmaf(a[j], B, b[j]);
+    const int t = first + j;
+    if (live && t < n_tokens) {
+      float a, b;
+      rglru_terms(gr[j] + cbr, gi[j] + cbi, uv[j], cc, &a, &b);
+      const int s = tok_seq[t];
+      if (t == seq_tok0[s]) {
+        b = fmaf(a, state[(size_t)seq_slot[s] * W + ch], b);
+        a = 0.f;
+      }
+      gates[(size_t)t * ldg + ch] = a;
+      gates[(size_t)t * ldg + W + ch] = b;
+      A *= a;
+      B = fmaf(a, B, b);
+    }
   }
   runA[warp][lane] = A;
   runB[warp][lane] = B;
@@ -95,16 +89,14 @@ rglru_compose_kernel(const float* __restrict__ gates, int ldg, const float* __re
   }
 }
 
-// Second pass: the state before the block's segment is the fold of the segments before it, in order (the step's first
-// token starts a sequence, so the fold starts from anything); the block walks its tokens from there, writes the outputs
-// and, at a sequence's last token, its state.
+// Second pass, over ab [tokens][2 W] = decays | inputs as the first left them: the state before the block's segment is the
+// fold of the segments before it, in order (the step's first token starts a sequence, so the fold may start from anything);
+// the block walks its tokens from there, writes the outputs and, at a sequence's last token, its state.
 template <typename TO>
 __global__ void __launch_bounds__(RG_WARPS * 32)
-rglru_walk_kernel(const float* __restrict__ gates, int ldg, const float* __restrict__ br, const float* __restrict__ bi,
-                  const float* __restrict__ u, int ldu, const float* __restrict__ c, const float* __restrict__ y, int ldy,
-                  const float* __restrict__ by, const float* __restrict__ seg, const float* __restrict__ init, float* __restrict__ state,
-                  TO* __restrict__ out, const int32_t* __restrict__ seq_tok0, const int32_t* __restrict__ seq_slot,
-                  const int32_t* __restrict__ tok_seq, int n_tokens, int W) {
+rglru_walk_kernel(const float* __restrict__ ab, int ldg, const float* __restrict__ y, int ldy, const float* __restrict__ by,
+                  const float* __restrict__ seg, float* __restrict__ state, TO* __restrict__ out, const int32_t* __restrict__ seq_tok0,
+                  const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ tok_seq, int n_tokens, int W) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float runA[RG_WARPS][32], runB[RG_WARPS][32];
@@ -113,16 +105,18 @@ rglru_walk_kernel(const float* __restrict__ gates, int ldg, const float* __restr
   const bool live = ch < W;
   const int first = g * RG_SEG + warp * RG_RUN;
   const float cby = live ? by[ch] : 0.f;
-  float yv[RG_RUN];          // the other branch's values, asked for before the arithmetic that they do not enter
+  float a[RG_RUN], b[RG_RUN], yv[RG_RUN];
 #pragma unroll
-  for (int j = 0; j < RG_RUN; ++j) yv[j] = (live && first + j < n_tokens) ? y[(size_t)(first + j) * ldy + ch] : 0.f;
+  for (int j = 0; j < RG_RUN; ++j) {
+    const bool on = live && first + j < n_tokens;
+    const size_t t = (size_t)(first + j);
+    a[j] = on ? ab[t * ldg + ch] : 1.f;
+    b[j] = on ? ab[t * ldg + W + ch] : 0.f;
+    yv[j] = on ? y[t * ldy + ch] : 0.f;
+  }
   float S = 0.f;
   if (live)
     for (int p = 0; p < g; ++p) S = fmaf(seg[((size_t)p * 2) * W + ch], S, seg[((size_t)p * 2 + 1) * W + ch]);
-  float a[RG_RUN], b[RG_RUN];
-  unsigned last;
-  rglru_run(gates, ldg, u, ldu, live ? c[ch] : 0.f, live ? br[ch] : 0.f, live ? bi[ch] : 0.f, init, false, seq_tok0, seq_slot, tok_seq,
-            first, n_tokens, W, ch, live, a, b, &last, nullptr);
   float A = 1.f, B = 0.f;
 #pragma unroll
   for (int j = 0; j < RG_RUN; ++j) {
@@ -139,7 +133,8 @@ rglru_walk_kernel(const float* __restrict__ gates, int ldg, const float* __restr
     S = fmaf(a[j], S, b[j]);
     if (live && t < n_tokens) {
       out[(size_t)t * W + ch] = from_f32<TO>(S * gelu_tanh_f(yv[j] + cby));
-      if (last >> j & 1) state[(size_t)seq_slot[tok_seq[t]] * W + ch] = S;
+      const int s = tok_seq[t];
+      if (t + 1 == seq_tok0[s + 1]) state[(size_t)seq_slot[s] * W + ch] = S;
     }
   }
 }
@@ -272,8 +267,8 @@ using namespace edgelm;
 
 // gates [tokens][>= 2 W] (r | i pre-activations, row pitch ldg), u [tokens][W..] (pitch ldu), y [tokens][W..] (pitch ldy);
 // `single`: every sequence brings one token (token t is sequence t).  Otherwise `tok_seq` [tokens] names every token's
-// sequence and `scratch` holds (n_seqs + 2 * segments) * W floats, segments = ceil(tokens / RG_SEG).
-extern "C" int edgelm_rglru_scan(const float* gates, int ldg, const float* br, const float* bi, const float* u, int ldu, const float* c,
+// sequence, `scratch` holds 2 * segments * W floats, segments = ceil(tokens / RG_SEG), and `gates` is overwritten (decays | inputs).
+extern "C" int edgelm_rglru_scan(float* gates, int ldg, const float* br, const float* bi, const float* u, int ldu, const float* c,
                                  const float* y, int ldy, const float* by, float* state, void* out, int out_dtype,
                                  const int32_t* seq_tok0, const int32_t* seq_slot, const int32_t* tok_seq, float* scratch, int n_seqs,
                                  int n_tokens, int W, int single, cudaStream_t stream) {
@@ -289,12 +284,11 @@ extern "C" int edgelm_rglru_scan(const float* gates, int ldg, const float* br, c
   } else {
     const int segs = (n_tokens + RG_SEG - 1) / RG_SEG;
     EL_REFUSE(tok_seq != nullptr && scratch != nullptr && segs <= 65535, "rglru_scan: a prompt step needs the tokens' sequences and scratch (%d segments)", segs);
-    float* init = scratch;
-    float* seg = scratch + (size_t)n_seqs * W;
+    float* seg = scratch;
     const dim3 grid((W + 31) / 32, segs), block(RG_WARPS * 32);
-    launch_pdl(bit, rglru_compose_kernel, grid, block, (size_t)0, stream, gates, ldg, br, bi, u, ldu, c, (const float*)state, seg, init, seq_tok0, seq_slot, tok_seq, n_tokens, W);
-    if (out_dtype == DT_F32) launch_pdl(bit, rglru_walk_kernel<float>, grid, block, (size_t)0, stream, gates, ldg, br, bi, u, ldu, c, y, ldy, by, (const float*)seg, (const float*)init, state, (float*)out, seq_tok0, seq_slot, tok_seq, n_tokens, W);
-    else launch_pdl(bit, rglru_walk_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, gates, ldg, br, bi, u, ldu, c, y, ldy, by, (const float*)seg, (const float*)init, state, (__nv_bfloat16*)out, seq_tok0, seq_slot, tok_seq, n_tokens, W);
+    launch_pdl(bit, rglru_compose_kernel, grid, block, (size_t)0, stream, gates, ldg, br, bi, u, ldu, c, (const float*)state, seg, seq_tok0, seq_slot, tok_seq, n_tokens, W);
+    if (out_dtype == DT_F32) launch_pdl(bit, rglru_walk_kernel<float>, grid, block, (size_t)0, stream, (const float*)gates, ldg, y, ldy, by, (const float*)seg, state, (float*)out, seq_tok0, seq_slot, tok_seq, n_tokens, W);
+    else launch_pdl(bit, rglru_walk_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, (const float*)gates, ldg, y, ldy, by, (const float*)seg, state, (__nv_bfloat16*)out, seq_tok0, seq_slot, tok_seq, n_tokens, W);
   }
   EL_LAUNCH_CHECK("rglru_scan");
   return 0;
