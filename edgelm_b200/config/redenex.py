@@ -1,8 +1,9 @@
 """The Redenex decoder's configuration, from its own config.json keys.
 
 config.json: `architecture` "Redenex", `vocab`, `width`, `norm.eps`, `embedding.scale`, `streams` (how many copies of the
-residual stream the layers keep; absent: one plain stream), `loop` {start, stop, times} (layers start .. stop - 1 run
-`times` times in a row with the same weights, every pass with a cache of its own; absent: every layer once) and `layers`,
+residual stream the layers keep; absent: one plain stream), `loop` {start, stop, times} (the stretch of layers from
+`start` up to but not including `stop` is repeated `times` times before the layers after it, the weights shared and every
+repetition with pages and states of its own; absent: every layer once) and `layers`,
 one entry per layer: `type` ("rglru" or "attention"), `mixer` (its sizes and constants) and `mlp` ({"kind": "dense", "ff",
 "limit"} or null for a layer without a feed-forward).  Optional: `max_positions`.  Tensors: `embed`, `l<i>.norm1`,
 `l<i>.norm2`, `l<i>.mix.*`, `l<i>.mlp.{gate,up,down}`, `l<i>.hc<q>.{in,out,mix}` (with `streams`), `final.norm`, `head`.

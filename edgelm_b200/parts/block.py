@@ -195,7 +195,7 @@ class HyperBlock(Part):
     the model's start).  For sublayer q (the mixer, then the feed-forward) with its tensors `in` [S], `out` [S] and `mix`
     [S, S] (indexed [from, to]):
 
-        u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] y     (all t at once, from the old x)
+        u = sum_s in[s] x_s;   y = sublayer(norm(u));   x'_t = sum_s mix[s, t] x_s + out[t] y     (every x' from the streams as they were)
 
     One kernel does a write and the read that follows it, also the next layer's (or the sum of the streams after the last
     layer): `ctx.streams_next` names that read, `ctx.streams_h` says that this layer's first read is done already.

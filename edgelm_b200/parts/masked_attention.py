@@ -15,9 +15,9 @@ and no value and is not scaled.  A value head may have another size than a key h
 the weighted values are float32 in both precisions; keys and values are kept in the compute dtype.
 
 Options, each with its constants in the spec:
-    conv      a short causal convolution over time on every channel of q, k and v right after the projection (taps
-              [channels, conv], last column the current token's, no bias, zeros before a sequence's start); the last
-              conv - 1 projected rows of a sequence are part of its state
+    conv      q, k and v each pass a depthwise causal filter over time straight after the projection:
+              out_t[c] = sum_j taps[c, j] * in_(t - conv + 1 + j)[c], no bias, inputs from before a sequence's start
+              counting as zero; the filter's memory, the previous conv - 1 projected rows, is kept per sequence as state
     qk_norm   {eps}: every query and key head (every map of it) is divided by its root mean square and multiplied by a
               weight of head_dim values that all heads share (`q_norm`, `k_norm`), before the rotation
     diff      {offset, eps}: "differential" attention.  A head has two maps, each with queries and keys of head_dim of its

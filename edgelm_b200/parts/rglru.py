@@ -1,13 +1,14 @@
 """A recurrent block around a real-gated linear recurrent unit: a diagonal recurrence whose decay depends on the input.
 
-Two branches of `width` channels from the mixer's input h: y = gelu_tanh(W_y h + b_y), and u = conv(W_x h + b_x), a causal
-convolution per channel (taps [width, taps], last column the current token's, a bias on the result, zeros before a
-sequence's start, no activation).  u is cut into `blocks` equal parts; in part b, with square matrices per part,
+The mixer's input h is projected twice to `width` channels.  One projection (with bias) goes through gelu_tanh and
+gates the output: y.  The other (with bias) goes through a depthwise causal filter over time, u_t[c] = cb[c] + sum_j
+taps[c, j] * x_(t - taps + 1 + j)[c] with x = 0 before a sequence's start and no activation.  The channels of u form
+`blocks` groups of width / blocks; group b has two square matrices R_b, I_b and bias vectors of its own:
 
     r = sigmoid(R_b u_b + br_b),   i = sigmoid(I_b u_b + bi_b)
-    log a = -decay_scale * r * softplus(lambda),   S_t = a S_(t-1) + sqrt(1 - a^2) * i * u      (S = 0 before the first token)
+    log a = -decay_scale * r * softplus(lambda),   S_t = a S_(t-1) + sqrt(1 - a^2) * i * u      (S_(-1) = 0; the first token is no exception)
 
-and the output is W_o (S * y).  A sequence's state: S (float32) and the convolution's last taps - 1 inputs.  The gates'
+and the mixer returns W_o (S * y).  A sequence's state: S (float32) and the convolution's last taps - 1 inputs.  The gates'
 products, the decay, the recurrence and its state are float32 in both precisions; the three projections run in the
 compute dtype and their float32 sums are kept.
 """
