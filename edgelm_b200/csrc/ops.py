@@ -503,7 +503,7 @@ def conv_act(u, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, n_seqs, upda
         _need(t is None or (t.dtype == torch.float32 and t.is_cuda and t.is_contiguous() and t.numel() == C), f"conv_act: {n}")
     _check(lib().edgelm_conv_act(_p(u), u.stride(0), int(off), _p(w), _p(b), _p(state), _p(out), _p(tok_seq), _p(seq_tok0), _p(seq_slot),
                                  T, int(n_seqs), C, taps, 1 if update_state else 0, _p(in_bias), 1 if act == "silu" else 0, _stream()),
-           launches=2 if taps > 1 and update_state else 1)
+           launches=2 if taps > 1 and update_state and T != int(n_seqs) else 1)      # (one token a sequence: the tail moves on in the same launch)
 
 
 def ssm_scan(xbc, u, dt_off, dt_bias, a_log, d, state, y, seq_tok0, seq_slot, n_seqs, heads, groups, n_state, head_dim,

@@ -58,18 +58,21 @@ __global__ void save_last_rows_kernel(const TIn* __restrict__ in, float* __restr
 // the state [slot][taps - 1][C] (oldest first; zeros before a sequence's start).  `u` holds the inputs at column
 // `off + c` of rows of `ldu` floats.  `in_bias` (optional): added to every input that `u` brings, before the
 // convolution (a projection's bias; the state keeps inputs with it, and the zeros before a sequence's start stay zeros).
-// `b` may be null (no bias on the result); `act` 0: no activation.
+// `b` may be null (no bias on the result); `act` 0: no activation.  `move_state` (steps of one token a sequence only: the
+// thread of (token, channel) is then the only one that touches the sequence's tail of that channel): the tail moves on
+// by the token's input here, and no second launch is needed.
 __global__ void conv_silu_kernel(const float* __restrict__ u, int ldu, int off, const float* __restrict__ w,
-                                 const float* __restrict__ b, const float* __restrict__ state, float* __restrict__ out,
+                                 const float* __restrict__ b, float* state, float* __restrict__ out,
                                  const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_tok0,
-                                 const int32_t* __restrict__ seq_slot, int C, int taps, const float* __restrict__ in_bias, int act) {
+                                 const int32_t* __restrict__ seq_slot, int C, int taps, const float* __restrict__ in_bias, int act,
+                                 int move_state) {
   pdl_launch_dependents();
   pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int t = blockIdx.x;
   const int s = tok_seq[t];
   const int t0 = seq_tok0[s];
   const int k = t - t0;
-  const float* st = state + (size_t)seq_slot[s] * (taps - 1) * C;
+  float* st = state + (size_t)seq_slot[s] * (taps - 1) * C;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {   // (few tokens: several blocks a token)
     float acc = b ? b[c] : 0.f;
     const float ib = in_bias ? in_bias[c] : 0.f;
@@ -79,6 +82,10 @@ __global__ void conv_silu_kernel(const float* __restrict__ u, int ldu, int off, 
       acc = fmaf(w[(size_t)c * taps + j], v, acc);
     }
     out[(size_t)t * C + c] = act ? silu_exact(acc) : acc;
+    if (move_state) {      // (k == 0: every row of the tail was read above; row j takes row j + 1, the last one the token's input)
+      for (int j = 0; j + 2 < taps; ++j) st[(size_t)j * C + c] = st[(size_t)(j + 1) * C + c];
+      st[(size_t)(taps - 2) * C + c] = u[(size_t)t * ldu + off + c] + ib;
+    }
   }
 }
 
@@ -514,9 +521,11 @@ extern "C" int edgelm_conv_act(const float* u, int ldu, int off, const float* w,
   // few tokens, 2 in prompt steps (one block a token there left a thread ten channels in a row at a width of 2,560)
   const int per_thread = n_tokens >= 256 ? 2 : 4;
   const int col_blocks = (C + per_thread * row_threads(C) - 1) / (per_thread * row_threads(C));
-  launch_pdl(pdl_bit_for_tokens(n_tokens), conv_silu_kernel, dim3(n_tokens, col_blocks), dim3(row_threads(C)), (size_t)(0), stream, u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, C, taps, in_bias, act);
+  // a step of one token a sequence (as many tokens as sequences) moves the tail on in the same launch
+  const int fused_tail = taps > 1 && update_state && n_tokens == n_seqs;
+  launch_pdl(pdl_bit_for_tokens(n_tokens), conv_silu_kernel, dim3(n_tokens, col_blocks), dim3(row_threads(C)), (size_t)(0), stream, u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, C, taps, in_bias, act, fused_tail);
   EL_LAUNCH_CHECK("conv_silu");
-  if (taps > 1 && update_state) {
+  if (taps > 1 && update_state && !fused_tail) {
     launch_pdl(pdl_bit_for_tokens(n_tokens), conv_state_update_kernel, dim3(dim3(n_seqs, (C + 255) / 256)), dim3(256), (size_t)(0), stream, u, ldu, off, state, seq_tok0, seq_slot, C, taps, in_bias);
     EL_LAUNCH_CHECK("conv_state_update");
   }
