@@ -70,7 +70,8 @@ def test_recurrent_unit_over_steps(W, blocks, taps, out_dtype):
 
 
 @pytest.mark.parametrize("w_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("W,blocks,T", [(96, 3, 37), (70, 2, 5), (33, 3, 1), (360, 5, 200), (480, 3, 131), (40, 1, 64)])
+@pytest.mark.parametrize("W,blocks,T", [(96, 3, 37), (70, 2, 5), (33, 3, 1), (360, 5, 200), (480, 3, 131), (40, 1, 64), (384, 4, 70), (256, 2, 33),
+                                       (400, 2, 65)])
 def test_gate_products_are_float32(W, blocks, T, w_dtype):
     """The block-diagonal gate products keep the float32 input's low bits (rounding the input to bfloat16 would miss by a
     thousand times the tolerance), for block widths that are odd, below a tile and several tiles."""
