@@ -173,7 +173,7 @@ __device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 lo, __nv_bfloat16 hi
   return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
 }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 rglru_gates_mma_kernel(const float* __restrict__ u, int ldu, const __nv_bfloat16* __restrict__ w_ra, const __nv_bfloat16* __restrict__ w_ri,
                        float* __restrict__ gates, int ldg, int n_tokens, int W, int bw) {
   pdl_launch_dependents();
@@ -184,18 +184,35 @@ rglru_gates_mma_kernel(const float* __restrict__ u, int ldu, const __nv_bfloat16
   const int t0 = blockIdx.x * GT_M, n0 = blockIdx.y * GT_N, blk = blockIdx.z;
   const float* ub = u + (size_t)blk * bw;
   float acc[8][4] = {};
-  for (int k0 = 0; k0 < bw; k0 += GT_KC) {
-    // the input: pairs of neighbours along K, each value split into three bfloat16 terms
-    for (int i = threadIdx.x; i < GT_M * (GT_KC / 2); i += 128) {
-      const int r = i / (GT_KC / 2), k = (i - r * (GT_KC / 2)) * 2;
-      const bool row = t0 + r < n_tokens;
-      float x[2];
+  // a chunk's global loads are issued a chunk ahead, into registers, and reach shared memory (the input split into its three
+  // terms on the way) when the chunk before has been multiplied: the loads' latency hides behind those multiply-adds
+  constexpr int A_IT = GT_M * (GT_KC / 2) / 128, W_IT = 2 * GT_N * GT_KC / 128;
+  float xa[A_IT][2];
+  __nv_bfloat16 xw[W_IT];
+  auto fetch = [&](int k0) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) x[e] = (row && k0 + k + e < bw) ? ub[(size_t)(t0 + r) * ldu + k0 + k + e] : 0.f;
+    for (int it = 0; it < A_IT; ++it) {
+      const int i = threadIdx.x + it * 128, r = i / (GT_KC / 2), k = (i - r * (GT_KC / 2)) * 2;
+      const bool row = t0 + r < n_tokens;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) xa[it][e] = (row && k0 + k + e < bw) ? ub[(size_t)(t0 + r) * ldu + k0 + k + e] : 0.f;
+    }
+#pragma unroll
+    for (int it = 0; it < W_IT; ++it) {      // rows n0 .. n0 + 31 of ra[blk], then of ri[blk]
+      const int i = threadIdx.x + it * 128, r = i / GT_KC, k = i - r * GT_KC, n = n0 + (r % GT_N);
+      const __nv_bfloat16* wm = r < GT_N ? w_ra : w_ri;
+      xw[it] = (n < bw && k0 + k < bw) ? wm[((size_t)blk * bw + n) * bw + k0 + k] : __float2bfloat16(0.f);
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < bw; k0 += GT_KC) {
+#pragma unroll
+    for (int it = 0; it < A_IT; ++it) {
+      const int i = threadIdx.x + it * 128, r = i / (GT_KC / 2), k = (i - r * (GT_KC / 2)) * 2;
       __nv_bfloat16 p[3][2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        float rest = x[e];
+        float rest = xa[it][e];
 #pragma unroll
         for (int q = 0; q < 3; ++q) {
           p[q][e] = __float2bfloat16(rest);
@@ -205,13 +222,13 @@ rglru_gates_mma_kernel(const float* __restrict__ u, int ldu, const __nv_bfloat16
 #pragma unroll
       for (int q = 0; q < 3; ++q) *reinterpret_cast<uint32_t*>(&As[q][r][k]) = pack_bf16(p[q][0], p[q][1]);
     }
-    // the weights: rows n0 .. n0 + 31 of ra[blk], then of ri[blk]
-    for (int i = threadIdx.x; i < 2 * GT_N * GT_KC; i += 128) {
-      const int r = i / GT_KC, k = i - r * GT_KC, n = n0 + (r % GT_N);
-      const __nv_bfloat16* wm = r < GT_N ? w_ra : w_ri;
-      Ws[r][k] = (n < bw && k0 + k < bw) ? wm[((size_t)blk * bw + n) * bw + k0 + k] : __float2bfloat16(0.f);
+#pragma unroll
+    for (int it = 0; it < W_IT; ++it) {
+      const int i = threadIdx.x + it * 128, r = i / GT_KC, k = i - r * GT_KC;
+      Ws[r][k] = xw[it];
     }
     __syncthreads();
+    if (k0 + GT_KC < bw) fetch(k0 + GT_KC);
 #pragma unroll
     for (int kk = 0; kk < GT_KC; kk += 16) {
       uint32_t af[3][4];
