@@ -4,6 +4,7 @@ from .llama import LlamaConfig
 from .sagizen import SagizenConfig
 from .vosulorn import VosulornConfig
 from .redenex import RedenexConfig
+from .radupel import RadupelConfig
 
 __all__ = ["ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "config_class_for", "read_config",
-           "register_architecture", "registered_architectures", "LlamaConfig", "SagizenConfig", "VosulornConfig", "RedenexConfig"]
+           "register_architecture", "registered_architectures", "LlamaConfig", "SagizenConfig", "VosulornConfig", "RedenexConfig", "RadupelConfig"]

@@ -59,9 +59,12 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  `reads_cache_of` is the index of an earlier schedule entry whose
-    cache this run's mixer reads (it then keeps none of its own)."""
+    cache this run's mixer reads (it then keeps none of its own).  `add_embedding`: right before this
+    run the embedding's output (the residual stream as it was before the first layer) is added to the
+    residual stream once more."""
     layer: int
     reads_cache_of: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -89,7 +92,7 @@ class ModelPlan:
         used = sorted({e.layer for e in schedule})
         renumber = {old: new for new, old in enumerate(used)}
         return dataclasses.replace(self, layers=tuple(self.layers[i] for i in used),
-                                   schedule=tuple(ScheduleEntry(renumber[e.layer], e.reads_cache_of) for e in schedule)).validate()
+                                   schedule=tuple(dataclasses.replace(e, layer=renumber[e.layer]) for e in schedule)).validate()
 
     def validate(self):
         if not self.layers or not self.schedule:
@@ -105,6 +108,8 @@ class ModelPlan:
                     raise ConfigError(f"schedule entry {i} reads the cache of entry {j}, which does not run before it")
                 if self.schedule[j].reads_cache_of is not None:
                     raise ConfigError(f"schedule entry {i} reads the cache of entry {j}, which keeps none itself")
+            if e.add_embedding and self.residual_streams != 1:
+                raise ConfigError(f"schedule entry {i} adds the embedding's output again, which several residual streams do not take")
         return self
 
 

@@ -63,7 +63,7 @@ rotate_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bi
                      const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table,
                      int table_stride, int n_pages, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int dk, int dv,
                      int rot, int interleaved, const double* __restrict__ freq, int* __restrict__ err, int maps,
-                     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps) {
+                     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, int ldq) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float ra_stage[];   // MA_WARPS rows of dk floats
@@ -79,8 +79,7 @@ rotate_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bi
     return;
   }
   const int in_page = pos % PAGE;
-  const int ld = H * dk + G * dk + G * dv;
-  const float* row = qkv + (size_t)t * ld;
+  const float* row = qkv + (size_t)t * ldq;       // (ldq: the rows' pitch; a row may hold more than q | k | v)
   float* sh = ra_stage + warp * dk;
   for (int head = blockIdx.y * MA_WARPS + warp; head < H + G; head += gridDim.y * MA_WARPS) {
     const float* src = row + (size_t)head * dk;
@@ -275,7 +274,7 @@ __global__ void __launch_bounds__(MA_MAX_WARPS * 32)
 masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vbase, int ldv,
                    const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table,
                    int table_stride, int n_pages, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
-                   const float* __restrict__ sink, int vec_k, int maps) {
+                   const float* __restrict__ sink, int vec_k, int maps, const float* __restrict__ gate, int ldg) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float ma_smem[];
@@ -345,7 +344,8 @@ masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* _
   for (int w2 = 0; w2 < NW; ++w2) M = fmaxf(M, wm[w2]);
   float L = sink ? expf(sink[h / maps] - M) : 0.f;
   for (int w2 = 0; w2 < NW; ++w2) L += wm[w2] == -INFINITY ? 0.f : wl[w2] * expf(wm[w2] - M);
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  float inv = L > 0.f ? 1.0f / L : 0.f;
+  if (gate) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h / maps]));      // the head's output gate: sigmoid of its logit
   for (int d = threadIdx.x; d < dv; d += blockDim.x) {
     float acc = 0.f;
     for (int w2 = 0; w2 < NW; ++w2)
@@ -403,7 +403,7 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
                          const int32_t* __restrict__ page_table, int table_stride, int n_pages, const int32_t* __restrict__ tile_seq,
                          const int32_t* __restrict__ tile_tok0, const int32_t* __restrict__ tile_ntok, const int32_t* __restrict__ tile_pos0,
                          int H, int G, int dk, int dv, float scale, int mask, int mask_size, const float* __restrict__ sink,
-                         int n_splits, float* __restrict__ part, int maps) {
+                         int n_splits, float* __restrict__ part, int maps, const float* __restrict__ gate, int ldg) {
   extern __shared__ float tm_smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -546,7 +546,8 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
       fix = m[r] == -INFINITY ? 0.f : expf(m[r] - mx);
       lr = lr * fix + expf(sk - mx);
     }
-    const float inv = lr > 0.f ? fix / lr : 0.f;
+    float inv = lr > 0.f ? fix / lr : 0.f;
+    if (gate) inv *= 1.0f / (1.0f + expf(-gate[(size_t)(tok0 + tok) * ldg + head]));      // the head's output gate
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
       const int d = lane + 32 * c;
@@ -558,7 +559,7 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
 // out[t][h][:] from the splits' partial results [t][h][split][2 + dv]: maxima, denominators, weighted values; the sink joins here
 template <typename TO>
 __global__ void masked_attn_fold_kernel(const float* __restrict__ part, TO* __restrict__ out, const float* __restrict__ sink, int H, int dv,
-                                        int n_splits) {
+                                        int n_splits, const float* __restrict__ gate, int ldg, int maps) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
@@ -570,7 +571,8 @@ __global__ void masked_attn_fold_kernel(const float* __restrict__ part, TO* __re
     const float ms = p[(size_t)s * (2 + dv)];
     if (ms != -INFINITY) L += p[(size_t)s * (2 + dv) + 1] * expf(ms - M);
   }
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  float inv = L > 0.f ? 1.0f / L : 0.f;
+  if (gate) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h / maps]));      // the head's output gate
   for (int d = threadIdx.x; d < dv; d += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < n_splits; ++s) {
@@ -626,8 +628,10 @@ extern "C" int edgelm_diff_combine(const float* a, void* out, int out_dtype, flo
 extern "C" int edgelm_rotate_append(const float* qkv, const float* bias, float* q_out, const int32_t* tok_pos, const int32_t* tok_seq,
                                     const int32_t* page_table, int table_stride, int n_pages, void* kcache, void* vcache, int dtype,
                                     int n_tokens, int H, int G, int dk, int dv, int rot, int interleaved, const double* freq, int* err,
-                                    int maps, const float* q_norm, const float* k_norm, float eps, cudaStream_t stream) {
+                                    int maps, const float* q_norm, const float* k_norm, float eps, int ldq, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
+  if (ldq == 0) ldq = (H + G) * dk + G * dv;
+  EL_REFUSE(ldq >= (H + G) * dk + G * dv, "rotate_append: rows of %d values do not hold the heads", ldq);
   EL_REFUSE(maps >= 1 && dk % maps == 0 && rot <= dk / maps, "rotate_append: %d maps of a head of %d with %d rotated dimensions", maps, dk, rot);
   EL_REFUSE(n_tokens > 0 && H > 0 && G > 0 && H % G == 0, "rotate_append: %d query heads over %d key/value heads", H, G);
   EL_REFUSE(dk >= 1 && dk <= 2048 && dv >= 1, "rotate_append: head sizes %d / %d are not taken", dk, dv);
@@ -637,10 +641,10 @@ extern "C" int edgelm_rotate_append(const float* qkv, const float* bias, float* 
   const int bit = pdl_bit_for_tokens(n_tokens);
   if (dtype == DT_F32)
     launch_pdl(bit, rotate_append_kernel<float>, grid, block, smem, stream, qkv, bias, q_out, tok_pos, tok_seq, page_table, table_stride,
-               n_pages, (float*)kcache, (float*)vcache, H, G, dk, dv, rot, interleaved, freq, err, maps, q_norm, k_norm, eps);
+               n_pages, (float*)kcache, (float*)vcache, H, G, dk, dv, rot, interleaved, freq, err, maps, q_norm, k_norm, eps, ldq);
   else if (dtype == DT_BF16)
     launch_pdl(bit, rotate_append_kernel<__nv_bfloat16>, grid, block, smem, stream, qkv, bias, q_out, tok_pos, tok_seq, page_table,
-               table_stride, n_pages, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, H, G, dk, dv, rot, interleaved, freq, err, maps, q_norm, k_norm, eps);
+               table_stride, n_pages, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, H, G, dk, dv, rot, interleaved, freq, err, maps, q_norm, k_norm, eps, ldq);
   else
     EL_REFUSE(false, "rotate_append: unknown dtype code %d", dtype);
   EL_LAUNCH_CHECK("rotate_append");
@@ -723,7 +727,7 @@ static int masked_common_check(const char* what, int H, int G, int dk, int dv, i
 template <typename T, typename TO, int DVR>
 static void launch_masked(const float* q, void* out, const void* kcache, const void* vcache, const int32_t* tok_pos, const int32_t* tok_seq,
                           const int32_t* page_table, int table_stride, int n_pages, int n_tokens, int H, int G, int dk, int dv, float scale,
-                          int mask, int mask_size, const float* sink, int warps, int maps, cudaStream_t stream) {
+                          int mask, int mask_size, const float* sink, int warps, int maps, const float* gate, int ldg, cudaStream_t stream) {
   const T* vb = vcache ? (const T*)vcache : (const T*)kcache;
   const int ldv = vcache ? dv : dk;
   const int vec_k = (dk % (16 / (int)sizeof(T)) == 0) && ((uintptr_t)kcache % 16 == 0);
@@ -731,7 +735,7 @@ static void launch_masked(const float* q, void* out, const void* kcache, const v
   auto kern = masked_attn_kernel<T, TO, DVR>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   launch_pdl(pdl_bit_for_tokens(n_tokens), kern, dim3(n_tokens, H * maps), dim3(warps * 32), smem, stream, q, (TO*)out, (const T*)kcache, vb, ldv,
-             tok_pos, tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, mask, mask_size, sink, vec_k, maps);
+             tok_pos, tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, mask, mask_size, sink, vec_k, maps, gate, ldg);
 }
 
 // `vcache` null: the values are the first dv dimensions of the key rows.  `max_keys`: the most keys a token of the step sees
@@ -740,13 +744,13 @@ static void launch_masked(const float* q, void* out, const void* kcache, const v
 extern "C" int edgelm_masked_attn(const float* q, void* out, int out_dtype, const void* kcache, const void* vcache, int dtype,
                                   const int32_t* tok_pos, const int32_t* tok_seq, const int32_t* page_table, int table_stride, int n_pages,
                                   int n_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size, const float* sink,
-                                  int max_keys, int maps, cudaStream_t stream) {
+                                  int max_keys, int maps, const float* gate, int ldg, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   if (masked_common_check("masked_attn", H, G, dk, dv, mask, mask_size, dtype, out_dtype)) return -1;
   EL_REFUSE(maps >= 1 && H * maps <= 65535 && (maps == 1 || (sink == nullptr && vcache != nullptr)), "masked_attn: %d maps take no sink and values of their own", maps);
   EL_REFUSE(vcache != nullptr || dv <= dk, "masked_attn: values of %d inside keys of %d", dv, dk);
   const int warps = max_keys <= 64 ? 2 : (max_keys <= 256 ? 4 : MA_MAX_WARPS);
-#define EL_MA2(T, TO, DVR) launch_masked<T, TO, DVR>(q, out, kcache, vcache, tok_pos, tok_seq, page_table, table_stride, n_pages, n_tokens, H, G, dk, dv, scale, mask, mask_size, sink, warps, maps, stream)
+#define EL_MA2(T, TO, DVR) launch_masked<T, TO, DVR>(q, out, kcache, vcache, tok_pos, tok_seq, page_table, table_stride, n_pages, n_tokens, H, G, dk, dv, scale, mask, mask_size, sink, warps, maps, gate, ldg, stream)
 #define EL_MA(DVR) do { if (dtype == DT_F32) EL_MA2(float, float, DVR); else if (out_dtype == DT_F32) EL_MA2(__nv_bfloat16, float, DVR); else EL_MA2(__nv_bfloat16, __nv_bfloat16, DVR); } while (0)
   if (dv <= 32) EL_MA(1); else if (dv <= 64) EL_MA(2); else if (dv <= 128) EL_MA(4); else if (dv <= 256) EL_MA(8); else EL_MA(16);
 #undef EL_MA
@@ -759,7 +763,8 @@ template <typename T, typename TO, int NC>
 static int launch_masked_tiled(const float* q, void* out, const void* kcache, const void* vcache, const int32_t* page_table, int table_stride,
                                int n_pages, const int32_t* tile_seq, const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0,
                                int n_tiles, int max_tile_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
-                               const float* sink, int n_splits, float* part, int n_tokens, int maps, cudaStream_t stream) {
+                               const float* sink, int n_splits, float* part, int n_tokens, int maps, const float* gate, int ldg,
+                               cudaStream_t stream) {
   const size_t smem = ((size_t)TM_KEYS * (dk + 1) + (vcache ? (size_t)TM_KEYS * dv : 0) + (size_t)TM_ROWS * dk + (size_t)TM_ROWS * TM_KEYS) * sizeof(float);
   EL_REFUSE(smem <= 227 * 1024, "masked_attn_tiled: heads of %d / %d need %zu bytes of shared memory", dk, dv, smem);
   auto kern = masked_attn_tiled_kernel<T, TO, NC>;
@@ -768,11 +773,11 @@ static int launch_masked_tiled(const float* q, void* out, const void* kcache, co
   const dim3 grid(n_tiles, G * maps, ((max_tile_tokens * grp + TM_ROWS - 1) / TM_ROWS) * n_splits);
   const int bit = pdl_bit_for_tokens(n_tokens);
   launch_pdl(bit, kern, grid, dim3(TM_WARPS * 32), smem, stream, q, (TO*)out, (const T*)kcache, (const T*)vcache, page_table, table_stride, n_pages,
-             tile_seq, tile_tok0, tile_ntok, tile_pos0, H, G, dk, dv, scale, mask, mask_size, sink, n_splits, part, maps);
+             tile_seq, tile_tok0, tile_ntok, tile_pos0, H, G, dk, dv, scale, mask, mask_size, sink, n_splits, part, maps, gate, ldg);
   if (n_splits > 1) {
     if (cudaGetLastError() != cudaSuccess) return 0;   // (the caller reports it)
     launch_pdl(bit, masked_attn_fold_kernel<TO>, dim3(n_tokens, H * maps), dim3(dv >= 256 ? 256 : 128), (size_t)0, stream, (const float*)part, (TO*)out, sink,
-               H * maps, dv, n_splits);
+               H * maps, dv, n_splits, gate, ldg, maps);
   }
   return 0;
 }
@@ -781,7 +786,8 @@ extern "C" int edgelm_masked_attn_tiled(const float* q, void* out, int out_dtype
                                         const int32_t* page_table, int table_stride, int n_pages, const int32_t* tile_seq,
                                         const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0, int n_tiles,
                                         int max_tile_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
-                                        const float* sink, int n_splits, float* part, int n_tokens, int maps, cudaStream_t stream) {
+                                        const float* sink, int n_splits, float* part, int n_tokens, int maps, const float* gate, int ldg,
+                                        cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   EL_REFUSE(maps >= 1 && G * maps <= 65535 && (maps == 1 || (sink == nullptr && vcache != nullptr)), "masked_attn_tiled: %d maps take no sink and values of their own", maps);
   EL_REFUSE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || part != nullptr) && n_tokens > 0, "masked_attn_tiled: %d splits", n_splits);
@@ -789,7 +795,7 @@ extern "C" int edgelm_masked_attn_tiled(const float* q, void* out, int out_dtype
   EL_REFUSE(n_tiles > 0 && max_tile_tokens > 0 && G <= 65535, "masked_attn_tiled: bad tile counts");
   EL_REFUSE(vcache != nullptr || dv <= dk, "masked_attn_tiled: values of %d inside keys of %d", dv, dk);
   int rc = 0;
-#define EL_MT2(T, TO, NC) rc = launch_masked_tiled<T, TO, NC>(q, out, kcache, vcache, page_table, table_stride, n_pages, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, H, G, dk, dv, scale, mask, mask_size, sink, n_splits, part, n_tokens, maps, stream)
+#define EL_MT2(T, TO, NC) rc = launch_masked_tiled<T, TO, NC>(q, out, kcache, vcache, page_table, table_stride, n_pages, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, H, G, dk, dv, scale, mask, mask_size, sink, n_splits, part, n_tokens, maps, gate, ldg, stream)
 #define EL_MT(NC) do { if (dtype == DT_F32) EL_MT2(float, float, NC); else if (out_dtype == DT_F32) EL_MT2(__nv_bfloat16, float, NC); else EL_MT2(__nv_bfloat16, __nv_bfloat16, NC); } while (0)
   if (dv <= 32) EL_MT(1); else if (dv <= 64) EL_MT(2); else if (dv <= 128) EL_MT(4); else if (dv <= 256) EL_MT(8); else EL_MT(16);
 #undef EL_MT

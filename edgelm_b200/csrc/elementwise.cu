@@ -115,6 +115,45 @@ rmsnorm_row_kernel(const float* __restrict__ x, const float* __restrict__ w, TOu
   }
 }
 
+// Two norms of the same rows (a layer whose sublayers both read the same x): the rows' statistics are computed once,
+//   y1 = x * inv * w1,  y2 = x * inv * w2   (w2, y2 may be null),
+// and with `add` the rows first receive another tensor's rows (x += add, written back): the residual stream taking an
+// earlier tensor in again right before a layer.  A block a row, two passes (the second finds the row in L1).
+template <typename TOut>
+__global__ void rmsnorm_pair_kernel(float* __restrict__ x, const float* __restrict__ add, const float* __restrict__ w1,
+                                    const float* __restrict__ w2, TOut* __restrict__ y1, TOut* __restrict__ y2, int dim, float eps) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  float* xr = x + (size_t)r * dim;
+  const float* ar = add ? add + (size_t)r * dim : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float v = xr[i];
+    if (ar) {
+      v += ar[i];
+      xr[i] = v;      // (the same thread reads it back below)
+    }
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = xr[i] * inv;
+    y1[(size_t)r * dim + i] = from_f32<TOut>(v * w1[i]);
+    if (y2) y2[(size_t)r * dim + i] = from_f32<TOut>(v * w2[i]);
+  }
+}
+
+// z <- cap * tanh(z / cap), in place
+__global__ void softcap_kernel(float* __restrict__ z, size_t n, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const float inv = 1.0f / cap;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) z[i] = cap * tanhf(z[i] * inv);
+}
+
 // ---------------------------------------------------------------- RoPE + cache append
 // qkv: [tokens, (nh + 2 nkv) * hd], the fused projection's output.  For every token: rotate
 // the nh query heads in place, rotate the nkv key heads and write them, with the raw value
@@ -260,6 +299,27 @@ extern "C" int edgelm_rmsnorm(const float* x, const float* w, void* y, int out_d
   } else
     EL_REFUSE(false, "rmsnorm: unknown dtype code %d", out_dtype);
   EL_LAUNCH_CHECK("rmsnorm");
+  return 0;
+}
+
+extern "C" int edgelm_rmsnorm_pair(float* x, const float* add, const float* w1, const float* w2, void* y1, void* y2, int out_dtype,
+                                   int rows, int dim, float eps, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  EL_REFUSE(rows > 0 && dim > 0 && (w2 == nullptr) == (y2 == nullptr), "rmsnorm_pair: bad sizes rows=%d dim=%d", rows, dim);
+  const dim3 grid(rows), block(dim >= 1024 ? 256 : 128);
+  if (out_dtype == DT_F32) launch_pdl(32, rmsnorm_pair_kernel<float>, grid, block, (size_t)0, stream, x, add, w1, w2, (float*)y1, (float*)y2, dim, eps);
+  else if (out_dtype == DT_BF16) launch_pdl(32, rmsnorm_pair_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, x, add, w1, w2, (__nv_bfloat16*)y1, (__nv_bfloat16*)y2, dim, eps);
+  else EL_REFUSE(false, "rmsnorm_pair: unknown dtype code %d", out_dtype);
+  EL_LAUNCH_CHECK("rmsnorm_pair");
+  return 0;
+}
+
+extern "C" int edgelm_softcap(float* z, long long n, float cap, cudaStream_t stream) {
+  if (n == 0) return 0;
+  EL_REFUSE(n > 0 && cap > 0.f, "softcap: bad sizes");
+  const long long blocks = (n + 255) / 256;
+  launch_pdl(32, softcap_kernel, dim3((unsigned)(blocks < 2048 ? blocks : 2048)), dim3(256), (size_t)0, stream, z, (size_t)n, cap);
+  EL_LAUNCH_CHECK("softcap");
   return 0;
 }
 

@@ -855,9 +855,11 @@ extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void*
 
 // A grouped product: a [M, K] with M a multiple of 128 (rows grouped, every group's first row at a multiple of 128),
 // w [n_groups * N, K] the groups' weights stacked; row tile t uses group tile_group[t] (negative: no rows).  out [M, N].
-// Epilogues: store (float32 or bfloat16) and SwiGLU (w2 the second stacked weight, bfloat16 out).
+// Epilogues: store (float32 or bfloat16) and the gated unit (w2 the second stacked weight, bfloat16 out; its form as in
+// `edgelm_gemm_tc_glu`: limit 0, alpha 1, shift 0 is SwiGLU).
 extern "C" int edgelm_gemm_tc_grouped(const void* a, int lda, const void* w, const void* w2, void* out, int ldo, int M, int N, int K,
-                                      int n_groups, const int32_t* tile_group, int out_dtype, int epilogue, int* err, cudaStream_t stream) {
+                                      int n_groups, const int32_t* tile_group, int out_dtype, int epilogue, float glu_limit, float glu_alpha,
+                                      float glu_shift, int* err, cudaStream_t stream) {
   if (M == 0) return 0;
   EL_REFUSE(M > 0 && M % TC_BM == 0 && N > 0 && K > 0 && n_groups > 0 && lda >= K && ldo >= N && tile_group != nullptr, "gemm_tc_grouped: bad sizes M=%d N=%d K=%d groups=%d", M, N, K, n_groups);
   EL_REFUSE(edgelm_gemm_tc_takes(a, lda, w, w2, K), "gemm_tc_grouped: K=%d and lda=%d must be multiples of 8 and the operands 16-byte aligned", K, lda);
@@ -875,8 +877,12 @@ extern "C" int edgelm_gemm_tc_grouped(const void* a, int lda, const void* w, con
   grp.tile_group = tile_group;
   grp.rows_per_group = N;
   int rc;
+  RopeAppend form{};
+  form.glu_limit = glu_limit;
+  form.glu_alpha = glu_alpha;
+  form.glu_shift = glu_shift;
   if (epilogue == TC_EPI_SWIGLU)
-    rc = launch_tc<64, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, nullptr, M, N, K, vec_ok, err, stream, false, RopeAppend{}, grp);
+    rc = launch_tc<64, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, nullptr, M, N, K, vec_ok, err, stream, false, form, grp);
   else if (out_dtype == DT_F32)
     rc = launch_tc<128, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, nullptr, M, N, K, vec_ok, err, stream, false, RopeAppend{}, grp);
   else

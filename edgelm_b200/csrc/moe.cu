@@ -2,6 +2,11 @@
 //
 //   route     logits z = Wr h + br in float32 (a block a token); the `top` largest (first maximum on ties), and their
 //             weights: the softmax over the chosen logits only.
+//   route_scored   another router on the same logits: scores s = softmax(z) over all experts; the choice looks at s + a
+//             correction per expert, optionally only inside the `keep` groups of neighbouring experts whose best corrected
+//             score is largest; the weights are the chosen experts' s over their sum, times a constant.  The last experts may
+//             be "identity experts" without weights (they give back their input): their pairs get no row, and `combine`
+//             adds the token's own input for them.  Extra router rows after the experts give per-token gates (sigmoid).
 //   plan      the (token, choice) pairs are grouped by expert: rows of a padded layout in which every expert's rows
 //             start at a multiple of the row tile, so that a tile of rows belongs to one expert.
 //             row_pair[row] = pair (token * top + choice) or -1; pair_row[pair] = its row; tile_expert[tile] = expert or -1.
@@ -16,20 +21,13 @@ namespace edgelm {
 
 constexpr int MOE_MAX_EXPERTS = 1024;
 
-// A block a token: its four warps share the width, eight experts at a time (the token's row is read once for the eight,
-// and a thread has eight independent sums and several steps of loads in flight); the warps' sums are added in a fixed order.
+// The router's logits of one token into shared memory: z[e] = wr[e] . h (+ br[e]).  A block a token: its four warps share the
+// width, eight experts at a time (the token's row is read once for the eight, and a thread has eight independent sums and
+// several steps of loads in flight); the warps' sums are added in a fixed order.  `part`: 32 floats.
 template <typename TH>
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br, int32_t* __restrict__ idx,
-                 float* __restrict__ wts, int n_tokens, int D, int E, int top) {
-  pdl_launch_dependents();
-  pdl_wait();
-  extern __shared__ float mr_smem[];         // [E] logits, then [4][8] partial sums
-  float* z = mr_smem;
-  float* part = mr_smem + E;
+__device__ __forceinline__ void moe_logits(const TH* __restrict__ row, const float* __restrict__ wr, const float* __restrict__ br,
+                                           float* z, float* part, int D, int E) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x;
-  const TH* row = h + (size_t)t * D;
   for (int e0 = 0; e0 < E; e0 += 8) {
     const float* w[8];
 #pragma unroll
@@ -48,9 +46,22 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ wr, const f
     }
     __syncthreads();
     if (threadIdx.x < 8 && e0 + threadIdx.x < E)
-      z[e0 + threadIdx.x] = ((part[threadIdx.x] + part[8 + threadIdx.x]) + (part[16 + threadIdx.x] + part[24 + threadIdx.x])) + br[e0 + threadIdx.x];
+      z[e0 + threadIdx.x] = ((part[threadIdx.x] + part[8 + threadIdx.x]) + (part[16 + threadIdx.x] + part[24 + threadIdx.x])) +
+                            (br ? br[e0 + threadIdx.x] : 0.f);
     __syncthreads();
   }
+}
+
+template <typename TH>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br, int32_t* __restrict__ idx,
+                 float* __restrict__ wts, int n_tokens, int D, int E, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float mr_smem[];         // [E] logits, then [4][8] partial sums
+  float* z = mr_smem;
+  moe_logits(h + (size_t)blockIdx.x * D, wr, br, z, mr_smem + E, D, E);
+  const int t = blockIdx.x;
   if (threadIdx.x == 0) {
     float zmax = 0.f, sum = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -68,6 +79,70 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ wr, const f
     }
     const float inv = 1.0f / sum;
     for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= inv;
+  }
+}
+
+// The scored router (see the head of this file).  E experts in all (the last ones may be identity experts: nothing here
+// treats them differently), `n_extra` more router rows whose sigmoid goes to extra[t][.].  Ties: the first of equal scores.
+template <typename TH>
+__global__ void __launch_bounds__(128)
+moe_route_scored_kernel(const TH* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ correction,
+                        int32_t* __restrict__ idx, float* __restrict__ wts, float* __restrict__ extra, int D, int E, int n_extra, int top,
+                        int groups, int keep, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float mr_smem[];         // [E + n_extra] logits, [E] choice scores, [groups] group scores, then [4][8] partial sums
+  float* z = mr_smem;
+  float* c = z + E + n_extra;
+  float* gs = c + E;
+  const int t = blockIdx.x;
+  moe_logits(h + (size_t)t * D, wr, (const float*)nullptr, z, gs + groups, D, E + n_extra);
+  if (threadIdx.x < n_extra) extra[(size_t)t * n_extra + threadIdx.x] = 1.0f / (1.0f + expf(-z[E + threadIdx.x]));
+  if (threadIdx.x == 0) {
+    float zmax = -INFINITY, sum = 0.f;
+    for (int e = 0; e < E; ++e) zmax = fmaxf(zmax, z[e]);
+    for (int e = 0; e < E; ++e) {
+      z[e] = expf(z[e] - zmax);
+      sum += z[e];
+    }
+    const float inv = 1.0f / sum;
+    for (int e = 0; e < E; ++e) {
+      z[e] *= inv;                                  // the score
+      c[e] = z[e] + (correction ? correction[e] : 0.f);   // what the choice looks at
+    }
+    if (groups > 1) {
+      const int size = E / groups;
+      for (int g = 0; g < groups; ++g) {
+        float b = -INFINITY;
+        for (int e = g * size; e < (g + 1) * size; ++e) b = fmaxf(b, c[e]);
+        gs[g] = b;
+      }
+      // a group is kept if fewer than `keep` groups come before it in the order (score descending, then index)
+      for (int g = 0; g < groups; ++g) {
+        int before = 0;
+        for (int o = 0; o < groups; ++o) before += (gs[o] > gs[g] || (gs[o] == gs[g] && o < g)) ? 1 : 0;
+        if (before >= keep)
+          for (int e = g * size; e < (g + 1) * size; ++e) c[e] = -INFINITY;
+      }
+    }
+    float picked = 0.f;
+    for (int k = 0; k < top; ++k) {
+      int best = -1;
+      float bc = -INFINITY;
+      for (int e = 0; e < E; ++e)
+        if (c[e] > bc) { bc = c[e]; best = e; }
+      if (best < 0) {       // (nothing left to choose from: fewer allowed experts than `top`, or NaN scores)
+        idx[(size_t)t * top + k] = -1;
+        wts[(size_t)t * top + k] = 0.f;
+        continue;
+      }
+      idx[(size_t)t * top + k] = best;
+      wts[(size_t)t * top + k] = z[best];
+      picked += z[best];
+      c[best] = -INFINITY;
+    }
+    const float norm = scale / (picked + 1e-20f);
+    for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= norm;
   }
 }
 
@@ -132,7 +207,8 @@ constexpr int MG_TM = 32, MG_TN = 64, MG_KC = 32;
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, const T* __restrict__ w2, void* __restrict__ out, int ldo,
-                const int32_t* __restrict__ row_pair, const int32_t* __restrict__ tile_expert, int top, int K, int N) {
+                const int32_t* __restrict__ row_pair, const int32_t* __restrict__ tile_expert, int top, int K, int N, float glu_limit,
+                float glu_alpha, float glu_shift) {
   pdl_launch_dependents();
   pdl_wait();
   const int e = tile_expert[blockIdx.x];
@@ -189,8 +265,13 @@ moe_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, const
       const int n = n0 + tx + 16 * j;
       if (n >= N) continue;
       if (GATED) {
-        const float z = acc[i][j];
-        ((T*)out)[(size_t)(r0 + r) * ldo + n] = from_f32<T>(z / (1.0f + expf(-z)) * acc2[i][j]);
+        // the gated unit: g sigmoid(alpha g) (v + shift), both branches clamped when there is a limit (none, 1, 0: SwiGLU)
+        float z = acc[i][j], v = acc2[i][j];
+        if (glu_limit > 0.f) {
+          z = fminf(z, glu_limit);
+          v = fminf(fmaxf(v, -glu_limit), glu_limit);
+        }
+        ((T*)out)[(size_t)(r0 + r) * ldo + n] = from_f32<T>(z / (1.0f + expf(-glu_alpha * z)) * (v + glu_shift));
       } else {
         ((float*)out)[(size_t)(r0 + r) * ldo + n] = acc[i][j];
       }
@@ -198,9 +279,13 @@ moe_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, const
   }
 }
 
-// x[t][:] += sum_k wts[t][k] * y[pair_row[t * top + k]][:]
+// x[t][:] += sum_k wts[t][k] * y[pair_row[t * top + k]][:]  (+ gate[t] * shared[t][:])
+// A pair without a row whose expert number is at least `n_real` is an identity expert's: its output is the token's own input
+// h[t] (in the type the experts read it in).
+template <typename TH>
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, int ldy, const float* __restrict__ wts,
-                                   const int32_t* __restrict__ pair_row, int top, int D) {
+                                   const int32_t* __restrict__ pair_row, int top, int D, const int32_t* __restrict__ idx, int n_real,
+                                   const TH* __restrict__ h, const float* __restrict__ shared, const float* __restrict__ gate) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -209,7 +294,9 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restric
     for (int k = 0; k < top; ++k) {
       const int r = pair_row[(size_t)t * top + k];
       if (r >= 0) acc = fmaf(wts[(size_t)t * top + k], y[(size_t)r * ldy + i], acc);
+      else if (idx && idx[(size_t)t * top + k] >= n_real) acc = fmaf(wts[(size_t)t * top + k], to_f32(h[(size_t)t * D + i]), acc);
     }
+    if (shared) acc = fmaf(gate ? gate[t] : 1.0f, shared[(size_t)t * D + i], acc);
     x[(size_t)t * D + i] += acc;
   }
 }
@@ -234,6 +321,23 @@ extern "C" int edgelm_moe_route(const void* h, int dtype, const float* wr, const
   return 0;
 }
 
+extern "C" int edgelm_moe_route_scored(const void* h, int dtype, const float* wr, const float* correction, int32_t* idx, float* wts,
+                                       float* extra, int n_tokens, int D, int E, int n_extra, int top, int groups, int keep, float scale,
+                                       cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && D > 0 && E >= 1 && E <= MOE_MAX_EXPERTS && top >= 1 && top <= E, "moe_route_scored: %d experts, %d chosen", E, top);
+  EL_REFUSE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups, "moe_route_scored: %d experts in %d groups, %d kept", E, groups, keep);
+  EL_REFUSE(n_extra >= 0 && n_extra <= 32 && (n_extra == 0 || extra != nullptr), "moe_route_scored: %d extra rows (up to 32)", n_extra);
+  const dim3 grid(n_tokens), block(128);
+  const size_t smem = (size_t)(2 * E + n_extra + groups + 32) * sizeof(float);
+  const int bit = pdl_bit_for_tokens(n_tokens);
+  if (dtype == DT_F32) launch_pdl(bit, moe_route_scored_kernel<float>, grid, block, smem, stream, (const float*)h, wr, correction, idx, wts, extra, D, E, n_extra, top, groups, keep, scale);
+  else if (dtype == DT_BF16) launch_pdl(bit, moe_route_scored_kernel<__nv_bfloat16>, grid, block, smem, stream, (const __nv_bfloat16*)h, wr, correction, idx, wts, extra, D, E, n_extra, top, groups, keep, scale);
+  else EL_REFUSE(false, "moe_route_scored: unknown dtype code %d", dtype);
+  EL_LAUNCH_CHECK("moe_route_scored");
+  return 0;
+}
+
 extern "C" int edgelm_moe_plan(const int32_t* idx, int n_pairs, int E, int tile_rows, int max_tiles, int32_t* row_pair, int32_t* pair_row,
                                int32_t* tile_expert, cudaStream_t stream) {
   if (n_pairs == 0) return 0;
@@ -247,12 +351,13 @@ extern "C" int edgelm_moe_plan(const int32_t* idx, int n_pairs, int E, int tile_
 // gated != 0: the gate and up products with the activation; a = the tokens' rows [tokens][K]; out = mid [rows][N] in `dtype`.
 // gated == 0: the down product; a = mid [rows][K]; out = y [rows][N] float32.
 extern "C" int edgelm_moe_gemm(const void* a, int lda, const void* w, const void* w2, void* out, int ldo, const int32_t* row_pair,
-                               const int32_t* tile_expert, int max_tiles, int top, int K, int N, int dtype, int gated, cudaStream_t stream) {
+                               const int32_t* tile_expert, int max_tiles, int top, int K, int N, int dtype, int gated, float glu_limit, float glu_alpha,
+                               float glu_shift, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   EL_REFUSE(max_tiles > 0 && K > 0 && N > 0 && top >= 1, "moe_gemm: bad sizes");
   const dim3 grid(max_tiles, (N + MG_TN - 1) / MG_TN), block(256);
   const int bit = pdl_bit_for_tokens(max_tiles);
-#define EL_MG(T, GATED) launch_pdl(bit, moe_gemm_kernel<T, GATED>, grid, block, (size_t)0, stream, (const T*)a, lda, (const T*)w, (const T*)w2, out, ldo, row_pair, tile_expert, top, K, N)
+#define EL_MG(T, GATED) launch_pdl(bit, moe_gemm_kernel<T, GATED>, grid, block, (size_t)0, stream, (const T*)a, lda, (const T*)w, (const T*)w2, out, ldo, row_pair, tile_expert, top, K, N, glu_limit, glu_alpha, glu_shift)
   if (dtype == DT_F32 && gated) EL_MG(float, true);
   else if (dtype == DT_F32) EL_MG(float, false);
   else if (dtype == DT_BF16 && gated) EL_MG(__nv_bfloat16, true);
@@ -274,11 +379,17 @@ extern "C" int edgelm_moe_gather_rows(const void* h, void* a, const int32_t* row
   return 0;
 }
 
+// `idx`, `n_real`, `h` (type `h_dtype`): the experts' numbers, how many of them have weights, and the tokens' inputs, for identity
+// experts (idx null: none).  `shared` [tokens][D] float32 with `gate` [tokens] (or null: 1): one more term for every token.
 extern "C" int edgelm_moe_combine(float* x, const float* y, int ldy, const float* wts, const int32_t* pair_row, int n_tokens, int top, int D,
+                                  const int32_t* idx, int n_real, const void* h, int h_dtype, const float* shared, const float* gate,
                                   cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  EL_REFUSE(n_tokens > 0 && top >= 1 && D > 0 && ldy >= D, "moe_combine: bad sizes");
-  launch_pdl(pdl_bit_for_tokens(n_tokens), moe_combine_kernel, dim3(n_tokens), dim3(D >= 1024 ? 256 : 128), (size_t)0, stream, x, y, ldy, wts, pair_row, top, D);
+  EL_REFUSE(n_tokens > 0 && top >= 1 && D > 0 && ldy >= D && (idx == nullptr || h != nullptr), "moe_combine: bad sizes");
+  const dim3 grid(n_tokens), block(D >= 1024 ? 256 : 128);
+  const int bit = pdl_bit_for_tokens(n_tokens);
+  if (h_dtype == DT_BF16) launch_pdl(bit, moe_combine_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, x, y, ldy, wts, pair_row, top, D, idx, n_real, (const __nv_bfloat16*)h, shared, gate);
+  else launch_pdl(bit, moe_combine_kernel<float>, grid, block, (size_t)0, stream, x, y, ldy, wts, pair_row, top, D, idx, n_real, (const float*)h, shared, gate);
   EL_LAUNCH_CHECK("moe_combine");
   return 0;
 }

@@ -550,14 +550,15 @@ def lowrank_decay(a, w2, w0, out):
     _check(lib().edgelm_lowrank_decay(_p(a), _p(w2), _dt(w2), _p(w0), _p(out), T, C, L, _stream()))
 
 
-def gated_group_norm(y, gate, w, out, groups, eps, gate_first):
-    """RMS norm of y [T, inner] in `groups` equal parts with weight w, gated by silu(gate) before the norm
-    (`gate_first`) or after it.  gate: float32 rows of any stride."""
+def gated_group_norm(y, gate, w, out, groups, eps, gate_first, gate_act="silu"):
+    """RMS norm of y [T, inner] in `groups` equal parts with weight w, gated by act(gate) before the norm
+    (`gate_first`) or after it; `gate_act` "silu" or "sigmoid".  gate: float32 rows of any stride."""
+    _need(gate_act in ("silu", "sigmoid"), "gated_group_norm: the gate's activation")
     _f32(y, "y"); _f32(w, "w")
     T, inner = y.shape
     _need(gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (T, inner) and out.is_contiguous() and out.shape == (T, inner), "gated_group_norm: shapes")
     _check(lib().edgelm_gated_group_norm(_p(y), _p(gate), gate.stride(0), _p(w), _p(out), _dt(out), T, inner, int(groups),
-                                         ctypes.c_float(eps), 1 if gate_first else 0, _stream()))
+                                         ctypes.c_float(eps), 1 if gate_first else 0, 1 if gate_act == "sigmoid" else 0, _stream()))
 
 
 def rmsnorm_add(x, y1, w, eps, a=1.0, y2=None, b=0.0, cast=None):
@@ -569,11 +570,11 @@ def rmsnorm_add(x, y1, w, eps, a=1.0, y2=None, b=0.0, cast=None):
                                     _dt(cast) if cast is not None else F32, x.shape[0], x.shape[1], ctypes.c_float(eps), _stream()))
 
 
-def scaled_sum(y1, a, y2, b, out):
-    """out = a y1 + b y2 (float32, equal shapes)."""
+def scaled_sum(y1, a, y2, b, out, add=False):
+    """out = a y1 + b y2 (float32, equal shapes); with `add`, out += a y1 + b y2."""
     _f32(y1, "y1"); _f32(y2, "y2"); _f32(out, "out")
     _need(y1.shape == y2.shape == out.shape, "scaled_sum: shapes")
-    _check(lib().edgelm_scaled_sum(_p(y1), ctypes.c_float(a), _p(y2), ctypes.c_float(b), _p(out), ctypes.c_longlong(out.numel()), _stream()))
+    _check(lib().edgelm_scaled_sum(_p(y1), ctypes.c_float(a), _p(y2), ctypes.c_float(b), _p(out), ctypes.c_longlong(out.numel()), 1 if add else 0, _stream()))
 
 
 def _pooled_cache_check(kcache, vcache, nkv, dk, dv, what):
@@ -665,9 +666,10 @@ def rotate_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache
     [T, nh dk] float32, keys and values to their places in the cache pages.  `maps` > 1: a head of dk dimensions is `maps`
     runs of dk / maps side by side, each rotated (its first `rot` dimensions) by itself.  `q_norm` / `k_norm` (float32
     [dk / maps]): every run is first divided by its root mean square (`eps` inside the root) and multiplied by the weight."""
-    _f32(qkv, "qkv"); _f32(q_out, "q_out")
+    _need(qkv.dtype == torch.float32 and qkv.is_cuda and qkv.dim() == 2 and qkv.stride(1) == 1, "rotate_append: qkv must be float32 rows")
+    _f32(q_out, "q_out")
     T = qkv.shape[0]
-    _need(qkv.shape[1] == (nh + nkv) * dk + nkv * dv and q_out.shape == (T, nh * dk), "rotate_append: shapes")
+    _need(qkv.shape[1] == (nh + nkv) * dk + nkv * dv and qkv.stride(0) >= qkv.shape[1] and q_out.shape == (T, nh * dk), "rotate_append: shapes")
     _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == qkv.shape[1]), "rotate_append: bias")
     _need(rot == 0 or (freq is not None and freq.dtype == torch.float64 and freq.numel() == rot // 2 and freq.is_contiguous()), "rotate_append: frequencies")
     _masked_cache_check(kcache, vcache, nkv, dk, dv, "rotate_append")
@@ -680,7 +682,7 @@ def rotate_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache
     _check(lib().edgelm_rotate_append(_p(qkv), _p(bias), _p(q_out), _p(tok_pos), _p(tok_seq), _p(page_table), page_table.stride(0),
                                       kcache.shape[0], _p(kcache), _p(vcache), _dt(kcache), T, nh, nkv, dk, dv, int(rot),
                                       1 if interleaved else 0, _p(freq), _p(err), int(maps), _p(q_norm), _p(k_norm), ctypes.c_float(eps),
-                                      _stream()))
+                                      qkv.stride(0), _stream()))
 
 
 def latent_prepare(u, kv_off, has_kv, q_out, q_pitch, q_off, copy_q, norm_w, eps, tok_pos, tok_seq, page_table, kcache, nh, d, rd, r, freq, err,
@@ -734,15 +736,21 @@ def add_row_bias(x, b):
     _check(lib().edgelm_add_row_bias(_p(x), _p(b), x.shape[0], x.shape[1], _stream()))
 
 
-def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, dk, dv, scale, mask, mask_size, sink, max_keys, maps=1):
+def _head_gate_check(gate, T, nh, what):
+    _need(gate is None or (gate.dtype == torch.float32 and gate.is_cuda and gate.shape == (T, nh) and gate.stride(1) == 1), f"{what}: the heads' gate")
+
+
+def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, dk, dv, scale, mask, mask_size, sink, max_keys, maps=1, gate=None):
     """Attention of every token of the step over the keys lo .. its position (`mask`: MASK_CAUSAL lo = 0; MASK_WINDOW the
     last `mask_size` keys; MASK_CHUNK the keys of its own chunk of `mask_size` positions).  q [T, nh dk] float32; out
     [T, nh dv] float32 or the cache's type; `vcache` None: a value is the first dv dimensions of its key row.  `sink`
     (float32 [nh] or None): one more term exp(sink_h) in the denominator.  `max_keys`: the most keys a token sees.
     `maps` > 1: every query head and key row holds `maps` runs of dk dimensions, each an attention of its own over the
-    head's values: q [T, nh maps dk], key rows of maps dk, out [T, nh maps dv] (no sink then)."""
+    head's values: q [T, nh maps dk], key rows of maps dk, out [T, nh maps dv] (no sink then).  `gate` (float32 [T, nh], rows of
+    any pitch): head h's output is multiplied by sigmoid(gate[t, h]) before it is rounded."""
     _f32(q, "q")
     T = q.shape[0]
+    _head_gate_check(gate, T, nh, "masked_attn")
     _need(q.shape == (T, nh * maps * dk) and out.is_contiguous() and out.shape == (T, nh * maps * dv), "masked_attn: shapes")
     _need(maps == 1 or (sink is None and vcache is not None), "masked_attn: several maps take no sink and values of their own")
     _masked_cache_check(kcache, vcache, nkv, dk * maps, dv, "masked_attn")
@@ -751,19 +759,20 @@ def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, d
         _i32(t, n)
     _check(lib().edgelm_masked_attn(_p(q), _p(out), _dt(out), _p(kcache), _p(vcache), _dt(kcache), _p(tok_pos), _p(tok_seq), _p(page_table),
                                     page_table.stride(0), kcache.shape[0], T, nh, nkv, dk, dv, ctypes.c_float(scale), int(mask), int(mask_size or 0),
-                                    _p(sink), int(max_keys), int(maps), _stream()))
+                                    _p(sink), int(max_keys), int(maps), _p(gate), gate.stride(0) if gate is not None else 0, _stream()))
 
 
 def masked_attn_tiled(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, nh, nkv,
-                      dk, dv, scale, mask, mask_size, sink, n_splits=1, part=None, maps=1):
+                      dk, dv, scale, mask, mask_size, sink, n_splits=1, part=None, maps=1, gate=None):
     """`masked_attn` for prompt steps: the step's tokens come as tiles (runs of at most `max_tile_tokens` consecutive tokens of
     one sequence); a page of keys and values is staged once for all the rows of a tile.  `page_table` None: `kcache` [T, nkv dk]
     and `vcache` [T, nkv dv] are the step's own keys and values, and every sequence of the step starts at position 0.
     `n_splits` > 1: the pages that a tile sees are dealt to so many blocks, whose partial results go through `part` (float32,
     T nh n_splits (2 + dv) values) and are merged by a second launch: for steps of few tokens over long sequences.
-    `maps` as in `masked_attn` (then `part` holds T nh maps n_splits (2 + dv) values)."""
+    `maps` and `gate` as in `masked_attn` (then `part` holds T nh maps n_splits (2 + dv) values)."""
     _f32(q, "q")
     T = q.shape[0]
+    _head_gate_check(gate, T, nh, "masked_attn_tiled")
     _need(q.shape == (T, nh * maps * dk) and out.is_contiguous() and out.shape == (T, nh * maps * dv), "masked_attn_tiled: shapes")
     _need(maps == 1 or (sink is None and vcache is not None), "masked_attn_tiled: several maps take no sink and values of their own")
     if page_table is not None:
@@ -781,7 +790,8 @@ def masked_attn_tiled(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, t
                                           page_table.stride(0) if page_table is not None else 0, kcache.shape[0] if page_table is not None else 0,
                                           _p(tile_seq), _p(tile_tok0), _p(tile_ntok), _p(tile_pos0), int(n_tiles),
                                           int(max_tile_tokens), nh, nkv, dk, dv, ctypes.c_float(scale), int(mask), int(mask_size or 0), _p(sink),
-                                          int(n_splits), _p(part), T, int(maps), _stream()), launches=2 if n_splits > 1 else 1)
+                                          int(n_splits), _p(part), T, int(maps), _p(gate), gate.stride(0) if gate is not None else 0, _stream()),
+           launches=2 if n_splits > 1 else 1)
 
 
 # ----------------------------------------------------------------------------- gated delta rule
@@ -830,6 +840,21 @@ def moe_route(h, wr, br, idx, wts, top):
     _check(lib().edgelm_moe_route(_p(h), _dt(h), _p(wr), _p(br), _p(idx), _p(wts), T, D, E, int(top), _stream()))
 
 
+def moe_route_scored(h, wr, correction, idx, wts, top, n_experts, groups=1, keep=1, scale=1.0, extra=None):
+    """The router that scores every expert: s = softmax(wr[:n_experts] h) over all experts (float32); the `top` experts with the
+    largest s + correction are chosen (first of equal ones), with `groups` > 1 only among the `keep` groups of neighbouring
+    experts whose best corrected score is largest; wts = s of the chosen over their sum (+ 1e-20), times `scale`.  Rows of
+    `wr` after the first `n_experts` give `extra` [T, rows] = sigmoid(row . h).  idx of a choice that could not be made: -1."""
+    _f32(wr, "router weight"); _f32(wts, "wts"); _i32(idx, "idx")
+    T, D = h.shape
+    n_extra = wr.shape[0] - n_experts
+    _need(h.is_contiguous() and wr.shape[1] == D and n_extra >= 0 and idx.shape == (T, top) and wts.shape == (T, top), "moe_route_scored: shapes")
+    _need(correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == n_experts), "moe_route_scored: correction")
+    _need((n_extra == 0) == (extra is None) and (extra is None or (extra.dtype == torch.float32 and extra.is_contiguous() and extra.shape == (T, n_extra))), "moe_route_scored: extra rows")
+    _check(lib().edgelm_moe_route_scored(_p(h), _dt(h), _p(wr), _p(correction), _p(idx), _p(wts), _p(extra), T, D, int(n_experts), int(n_extra), int(top),
+                                         int(groups), int(keep), ctypes.c_float(scale), _stream()))
+
+
 def moe_plan(idx, n_experts, tile_rows, row_pair, pair_row, tile_expert):
     """Group the pairs of idx [T, top] by expert: row_pair [max_tiles * tile_rows] (pair or -1), pair_row [T * top] (each
     pair's row), tile_expert [max_tiles] (the expert of a tile of rows, or -1)."""
@@ -846,15 +871,19 @@ def moe_gather_rows(h, a, row_pair, top):
     _check(lib().edgelm_moe_gather_rows(_p(h), _p(a), _p(row_pair), row_pair.numel(), int(top), h.shape[1], _dt(h), _stream()))
 
 
-def moe_gate_up(h, w_gate, w_up, mid, row_pair, tile_expert, top):
-    """mid[row] = silu(w_gate[e] h[t]) * (w_up[e] h[t]) for every row of the plan (t = row_pair[row] // top, e the row's tile's
-    expert), on the CUDA cores."""
+GLU_SWIGLU = (0.0, 1.0, 0.0)     # (limit, alpha, shift) of the gated unit g sigmoid(alpha g) (v + shift); limit 0: no clamps
+
+
+def moe_gate_up(h, w_gate, w_up, mid, row_pair, tile_expert, top, glu=GLU_SWIGLU):
+    """mid[row] = unit(w_gate[e] h[t], w_up[e] h[t]) for every row of the plan (t = row_pair[row] // top, e the row's tile's
+    expert), on the CUDA cores.  The unit is silu(g) * v, or with `glu` (limit, alpha, shift) g sigmoid(alpha g) (v + shift) with
+    g = min(g, limit) and v = clamp(v, -limit, limit) when limit > 0."""
     E, N, K = w_gate.shape
     _need(h.dtype == w_gate.dtype == w_up.dtype == mid.dtype and h.is_contiguous() and w_gate.is_contiguous() and w_up.is_contiguous() and mid.is_contiguous(), "moe_gate_up: layout")
     _need(h.shape[1] == K and w_up.shape == w_gate.shape and mid.shape == (row_pair.numel(), N), "moe_gate_up: shapes")
     _need(row_pair.numel() == tile_expert.numel() * moe_tile_rows(), "moe_gate_up: the plan's row tile is not this kernel's")
     _check(lib().edgelm_moe_gemm(_p(h), h.stride(0), _p(w_gate), _p(w_up), _p(mid), mid.stride(0), _p(row_pair), _p(tile_expert),
-                                 tile_expert.numel(), int(top), K, N, _dt(h), 1, _stream()))
+                                 tile_expert.numel(), int(top), K, N, _dt(h), 1, ctypes.c_float(glu[0]), ctypes.c_float(glu[1]), ctypes.c_float(glu[2]), _stream()))
 
 
 def moe_down(mid, w_down, y, row_pair, tile_expert, top):
@@ -864,7 +893,7 @@ def moe_down(mid, w_down, y, row_pair, tile_expert, top):
     _need(mid.dtype == w_down.dtype and mid.is_contiguous() and w_down.is_contiguous() and mid.shape == (row_pair.numel(), K) and y.shape == (row_pair.numel(), N), "moe_down: shapes")
     _need(row_pair.numel() == tile_expert.numel() * moe_tile_rows(), "moe_down: the plan's row tile is not this kernel's")
     _check(lib().edgelm_moe_gemm(_p(mid), mid.stride(0), _p(w_down), _p(None), _p(y), y.stride(0), _p(row_pair), _p(tile_expert),
-                                 tile_expert.numel(), int(top), K, N, _dt(mid), 0, _stream()))
+                                 tile_expert.numel(), int(top), K, N, _dt(mid), 0, ctypes.c_float(0.0), ctypes.c_float(1.0), ctypes.c_float(0.0), _stream()))
 
 
 def gemm_tc_grouped_takes(a, w, w2=None):
@@ -874,24 +903,35 @@ def gemm_tc_grouped_takes(a, w, w2=None):
     return bool(lib().edgelm_gemm_tc_takes(_p(a), a.stride(0), _p(w), _p(w2), a.shape[1]))
 
 
-def gemm_tc_grouped(a, w, out, tile_group, err, epilogue=EPI_STORE, w2=None):
+def gemm_tc_grouped(a, w, out, tile_group, err, epilogue=EPI_STORE, w2=None, glu=GLU_SWIGLU):
     """out[row] = a[row] @ w[g].T (+ epilogue) with g = tile_group[row // 128] (negative: a tile without rows): a [M, K]
-    bfloat16 with M a multiple of 128, w (and w2 for SwiGLU) [groups, N, K] bfloat16, out [M, N] float32 or bfloat16."""
+    bfloat16 with M a multiple of 128, w (and w2 for the gated unit) [groups, N, K] bfloat16, out [M, N] float32 or bfloat16.
+    `glu`: the gated unit's form, as in `moe_gate_up`."""
     _i32(tile_group, "tile_group")
     G, N, K = w.shape
     M = a.shape[0]
     _need(a.shape == (M, K) and out.shape == (M, N) and out.stride(1) == 1 and tile_group.numel() * 128 == M, "gemm_tc_grouped: shapes")
     _need(w2 is None or (w2.shape == w.shape and w2.is_contiguous() and w2.dtype == w.dtype), "gemm_tc_grouped: second weight")
     _check(lib().edgelm_gemm_tc_grouped(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), M, N, K, G, _p(tile_group), _dt(out), int(epilogue),
-                                        _p(err), _stream()))
+                                        ctypes.c_float(glu[0]), ctypes.c_float(glu[1]), ctypes.c_float(glu[2]), _p(err), _stream()))
 
 
-def moe_combine(x, y, wts, pair_row):
-    """x[t] += sum_k wts[t, k] * y[pair_row[t * top + k]]."""
+def moe_combine(x, y, wts, pair_row, idx=None, n_real=0, h=None, shared=None, gate=None):
+    """x[t] += sum_k wts[t, k] * y[pair_row[t * top + k]].  With `idx` [T, top], `n_real` and `h` [T, D]: a pair whose expert
+    number is at least `n_real` belongs to an identity expert, whose output is the token's input h[t].  With `shared`
+    [T, D] float32 (and `gate` [T] float32, else 1): x[t] += gate[t] * shared[t] as well."""
     _f32(x, "x"); _f32(y, "y"); _f32(wts, "wts"); _i32(pair_row, "pair_row")
     T, top = wts.shape
-    _need(x.shape[0] == T and y.shape[1] == x.shape[1] and pair_row.numel() == T * top, "moe_combine: shapes")
-    _check(lib().edgelm_moe_combine(_p(x), _p(y), y.stride(0), _p(wts), _p(pair_row), T, top, x.shape[1], _stream()))
+    D = x.shape[1]
+    _need(x.shape[0] == T and y.shape[1] == D and pair_row.numel() == T * top, "moe_combine: shapes")
+    if idx is not None:
+        _i32(idx, "idx")
+        _need(idx.numel() == T * top and h is not None and h.is_contiguous() and h.shape == (T, D), "moe_combine: identity experts need the tokens' inputs")
+    if shared is not None:
+        _f32(shared, "shared")
+        _need(shared.shape == (T, D) and (gate is None or (gate.dtype == torch.float32 and gate.is_contiguous() and gate.numel() == T)), "moe_combine: the shared term")
+    _check(lib().edgelm_moe_combine(_p(x), _p(y), y.stride(0), _p(wts), _p(pair_row), T, top, D, _p(idx), int(n_real), _p(h if idx is not None else None),
+                                    _dt(h) if idx is not None else F32, _p(shared), _p(gate if shared is not None else None), _stream()))
 
 
 # ----------------------------------------------------------------------------- several residual streams
@@ -967,12 +1007,14 @@ def rglru_gates(u, w_ra, w_ri, gates, blocks):
         head_matmul(u, bw, w_ri, gates[:, W:], bw)
 
 
-def clamped_glu(gu, mid, limit, alpha):
-    """mid = g sigmoid(alpha g) (v + 1) with g = min(gate, limit), v = clamp(up, -limit, limit); gu [T, 2 F] float32 = gate | up."""
+def clamped_glu(gu, mid, limit, alpha, shift=1.0, bias=None):
+    """mid = g sigmoid(alpha g) (v + shift) with g = min(gate, limit), v = clamp(up, -limit, limit) (limit 0: no clamps);
+    gu [T, 2 F] float32 = gate | up, `bias` [2 F] float32 added to it first.  limit 0, alpha 1, shift 0: silu(gate) * up."""
     _f32(gu, "gu")
     T, F = mid.shape
     _need(gu.shape == (T, 2 * F) and mid.is_contiguous(), "clamped_glu: shapes")
-    _check(lib().edgelm_clamped_glu(_p(gu), _p(mid), _dt(mid), T, F, ctypes.c_float(limit), ctypes.c_float(alpha), _stream()))
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_cuda and bias.is_contiguous() and bias.numel() == 2 * F), "clamped_glu: bias")
+    _check(lib().edgelm_clamped_glu(_p(gu), _p(mid), _dt(mid), T, F, ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift), _p(bias), _stream()))
 
 
 def diff_combine(a, out, lam, eps, post, w=None):
@@ -985,3 +1027,41 @@ def diff_combine(a, out, lam, eps, post, w=None):
     _need(w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == dv), "diff_combine: weight")
     _check(lib().edgelm_diff_combine(_p(a), _p(out), _dt(out), ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(post), _p(w),
                                      T * a.shape[1], dv, _stream()))
+
+
+# ----------------------------------------------------------------------------- linear attention with a constant decay per head
+def silu_columns(u, off, n):
+    """u[:, off : off + n] <- silu(.) in place (float32 rows of any pitch)."""
+    _need(u.dtype == torch.float32 and u.is_cuda and u.dim() == 2 and u.stride(1) == 1 and 0 <= off and off + n <= u.shape[1], "silu_columns: layout")
+    _check(lib().edgelm_silu_columns(_p(u), u.stride(0), int(off), int(n), u.shape[0], _stream()))
+
+
+def decay_scan(u, q_off, k_off, v_off, decay, state, o, seq_tok0, seq_slot, n_seqs, heads, k_dim, v_dim):
+    """Per head S <- decay_h S + k_t v_t^T, then o_t = S^T q_t, over the step's tokens in order.  q, k (heads x k_dim) and v
+    (heads x v_dim) are columns of u [T, *] float32 from q_off, k_off, v_off; decay [heads] float32; state [slots, heads,
+    v_dim, k_dim] float32; o [T, heads v_dim] float32."""
+    _f32(decay, "decay"); _f32(state, "state"); _f32(o, "o")
+    _i32(seq_tok0, "seq_tok0"); _i32(seq_slot, "seq_slot")
+    T = u.shape[0]
+    _need(u.dtype == torch.float32 and u.is_cuda and u.stride(1) == 1, "decay_scan: u must be float32 rows")
+    _need(max(q_off, k_off) + heads * k_dim <= u.shape[1] and v_off + heads * v_dim <= u.shape[1] and o.shape == (T, heads * v_dim), "decay_scan: shapes")
+    _need(decay.numel() == heads and tuple(state.shape[1:]) == (heads, v_dim, k_dim), "decay_scan: decay or state")
+    _check(lib().edgelm_decay_scan(_p(u), u.stride(0), int(q_off), int(k_off), int(v_off), _p(decay), _p(state), _p(o), _p(seq_tok0), _p(seq_slot),
+                                   int(n_seqs), int(heads), int(k_dim), int(v_dim), T, _stream()))
+
+
+def rmsnorm_pair(x, w1, eps, y1, w2=None, y2=None, add=None):
+    """y1 = norm(x) * w1 and y2 = norm(x) * w2 with the rows' statistics computed once; with `add` [T, D] float32, x += add first
+    (written back).  x float32 [T, D]; y1, y2 in the compute dtype."""
+    _f32(x, "x"); _f32(w1, "w1")
+    _need(y1.shape == x.shape and y1.is_contiguous() and w1.numel() == x.shape[1], "rmsnorm_pair: shapes")
+    _need((w2 is None) == (y2 is None) and (w2 is None or (w2.dtype == torch.float32 and w2.is_contiguous() and w2.numel() == x.shape[1] and
+                                                            y2.shape == x.shape and y2.is_contiguous() and y2.dtype == y1.dtype)), "rmsnorm_pair: the second norm")
+    _need(add is None or (add.dtype == torch.float32 and add.is_contiguous() and add.shape == x.shape), "rmsnorm_pair: the rows to add")
+    _check(lib().edgelm_rmsnorm_pair(_p(x), _p(add), _p(w1), _p(w2), _p(y1), _p(y2), _dt(y1), x.shape[0], x.shape[1], ctypes.c_float(eps), _stream()))
+
+
+def softcap(z, cap):
+    """z <- cap * tanh(z / cap), in place (float32)."""
+    _f32(z, "z")
+    _check(lib().edgelm_softcap(_p(z), ctypes.c_longlong(z.numel()), ctypes.c_float(cap), _stream()))

@@ -408,12 +408,13 @@ __global__ void lowrank_decay_kernel(const float* __restrict__ a, const TW* __re
 
 // ------------------------------------------------------------------ gated RMS norm in equal groups
 // A row of `inner` values in `groups` equal parts, each divided by its own root mean square.
-//   gate_first:  v = y * silu(gate); out = v / rms(v) * w
-//   else:        out = y / rms(y) * w * silu(gate)
+//   gate_first:  v = y * act(gate); out = v / rms(v) * w
+//   else:        out = y / rms(y) * w * act(gate)
+// act = silu, or with `gate_sigmoid` the sigmoid itself.
 template <typename TOut>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ gate, int ldg,
                                         const float* __restrict__ w, TOut* __restrict__ out, int inner, int groups, float eps,
-                                        int gate_first) {
+                                        int gate_first, int gate_sigmoid) {
   pdl_launch_dependents();
   pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   __shared__ float red[33];
@@ -423,14 +424,14 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
   const float* wr = w + (size_t)g * gs;
   float ss = 0.f;
   for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-    const float v = gate_first ? yr[i] * silu_exact(gr[i]) : yr[i];
+    const float v = gate_first ? yr[i] * (gate_sigmoid ? 1.0f / (1.0f + expf(-gr[i])) : silu_exact(gr[i])) : yr[i];
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
   TOut* orow = out + (size_t)t * inner + (size_t)g * gs;
   for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-    const float sg = silu_exact(gr[i]);
+    const float sg = gate_sigmoid ? 1.0f / (1.0f + expf(-gr[i])) : silu_exact(gr[i]);
     orow[i] = from_f32<TOut>(gate_first ? yr[i] * sg * inv * wr[i] : yr[i] * inv * wr[i] * sg);
   }
 }
@@ -461,22 +462,25 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ x, const float* __restric
   }
 }
 
-// out = a y1 + b y2
-__global__ void scaled_sum_kernel(const float* __restrict__ y1, float a, const float* __restrict__ y2, float b, float* __restrict__ out, size_t n) {
+// out = a y1 + b y2, or with `add` out += a y1 + b y2
+__global__ void scaled_sum_kernel(const float* __restrict__ y1, float a, const float* __restrict__ y2, float b, float* __restrict__ out, size_t n, int add) {
   pdl_launch_dependents();
   pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = a * y1[i] + b * y2[i];
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = a * y1[i] + b * y2[i];
+    out[i] = add ? out[i] + v : v;
+  }
 }
 
 }  // namespace edgelm
 
 using namespace edgelm;
 
-extern "C" int edgelm_scaled_sum(const float* y1, float a, const float* y2, float b, float* out, long long n, cudaStream_t stream) {
+extern "C" int edgelm_scaled_sum(const float* y1, float a, const float* y2, float b, float* out, long long n, int add, cudaStream_t stream) {
   if (n == 0) return 0;
   EL_REFUSE(n > 0, "scaled_sum: bad size");
   const long long blocks = (n + 255) / 256;
-  scaled_sum_kernel<<<(unsigned)(blocks < 4096 ? blocks : 4096), 256, 0, stream>>>(y1, a, y2, b, out, (size_t)n);
+  scaled_sum_kernel<<<(unsigned)(blocks < 4096 ? blocks : 4096), 256, 0, stream>>>(y1, a, y2, b, out, (size_t)n, add);
   EL_LAUNCH_CHECK("scaled_sum");
   return 0;
 }
@@ -603,12 +607,12 @@ extern "C" int edgelm_lowrank_decay(const float* a, const void* w2, int w_dtype,
 }
 
 extern "C" int edgelm_gated_group_norm(const float* y, const float* gate, int ldg, const float* w, void* out, int out_dtype,
-                                       int n_tokens, int inner, int groups, float eps, int gate_first, cudaStream_t stream) {
+                                       int n_tokens, int inner, int groups, float eps, int gate_first, int gate_sigmoid, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && inner > 0 && groups > 0 && inner % groups == 0, "gated_group_norm: %d values do not split into %d equal groups", inner, groups);
   const dim3 grid(n_tokens, groups), block(inner / groups >= 1024 ? 256 : (inner / groups >= 128 ? 128 : 32));
-  if (out_dtype == DT_F32) launch_pdl(pdl_bit_for_tokens(n_tokens), gated_group_norm_kernel<float>, dim3(grid), dim3(block), (size_t)(0), stream, y, gate, ldg, w, (float*)out, inner, groups, eps, gate_first);
-  else if (out_dtype == DT_BF16) launch_pdl(pdl_bit_for_tokens(n_tokens), gated_group_norm_kernel<__nv_bfloat16>, dim3(grid), dim3(block), (size_t)(0), stream, y, gate, ldg, w, (__nv_bfloat16*)out, inner, groups, eps, gate_first);
+  if (out_dtype == DT_F32) launch_pdl(pdl_bit_for_tokens(n_tokens), gated_group_norm_kernel<float>, dim3(grid), dim3(block), (size_t)(0), stream, y, gate, ldg, w, (float*)out, inner, groups, eps, gate_first, gate_sigmoid);
+  else if (out_dtype == DT_BF16) launch_pdl(pdl_bit_for_tokens(n_tokens), gated_group_norm_kernel<__nv_bfloat16>, dim3(grid), dim3(block), (size_t)(0), stream, y, gate, ldg, w, (__nv_bfloat16*)out, inner, groups, eps, gate_first, gate_sigmoid);
   else EL_REFUSE(false, "gated_group_norm: unknown dtype code %d", out_dtype);
   EL_LAUNCH_CHECK("gated_group_norm");
   return 0;

@@ -268,13 +268,18 @@ rglru_gates_mma_kernel(const float* __restrict__ u, int ldu, const __nv_bfloat16
 
 // mid = g sigmoid(alpha g) (v + 1) with g = min(gate, limit), v = clamp(up, -limit, limit); gu [tokens][2 F] float32 = gate | up
 template <typename TO>
-__global__ void clamped_glu_kernel(const float* __restrict__ gu, TO* __restrict__ mid, int F, float limit, float alpha) {
+__global__ void clamped_glu_kernel(const float* __restrict__ gu, TO* __restrict__ mid, int F, float limit, float alpha, float shift,
+                                   const float* __restrict__ bias) {
   pdl_launch_dependents();
   pdl_wait();
   const float* row = gu + (size_t)blockIdx.x * 2 * F;
   for (int i = threadIdx.x; i < F; i += blockDim.x) {
-    const float g = fminf(row[i], limit), v = fminf(fmaxf(row[F + i], -limit), limit);
-    mid[(size_t)blockIdx.x * F + i] = from_f32<TO>(g * sigmoid_f(alpha * g) * (v + 1.0f));
+    float g = row[i] + (bias ? bias[i] : 0.f), v = row[F + i] + (bias ? bias[F + i] : 0.f);
+    if (limit > 0.f) {
+      g = fminf(g, limit);
+      v = fminf(fmaxf(v, -limit), limit);
+    }
+    mid[(size_t)blockIdx.x * F + i] = from_f32<TO>(g * sigmoid_f(alpha * g) * (v + shift));
   }
 }
 
@@ -324,13 +329,16 @@ extern "C" int edgelm_rglru_gates(const float* u, int ldu, const void* w_ra, con
   return 0;
 }
 
-extern "C" int edgelm_clamped_glu(const float* gu, void* mid, int out_dtype, int n_tokens, int F, float limit, float alpha, cudaStream_t stream) {
+// mid = g sigmoid(alpha g) (v + shift) with g = gate + bias, v = up + bias, both clamped (g from above, v on both sides) when
+// limit > 0; `bias` [2 F] may be null.  limit 0, alpha 1, shift 0: SwiGLU.
+extern "C" int edgelm_clamped_glu(const float* gu, void* mid, int out_dtype, int n_tokens, int F, float limit, float alpha, float shift,
+                                  const float* bias, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  EL_REFUSE(n_tokens > 0 && F > 0 && limit > 0.f, "clamped_glu: bad sizes");
+  EL_REFUSE(n_tokens > 0 && F > 0 && limit >= 0.f, "clamped_glu: bad sizes");
   const dim3 grid(n_tokens), block(F >= 1024 ? 256 : 128);
   const int bit = pdl_bit_for_tokens(n_tokens);
-  if (out_dtype == DT_F32) launch_pdl(bit, clamped_glu_kernel<float>, grid, block, (size_t)0, stream, gu, (float*)mid, F, limit, alpha);
-  else if (out_dtype == DT_BF16) launch_pdl(bit, clamped_glu_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, gu, (__nv_bfloat16*)mid, F, limit, alpha);
+  if (out_dtype == DT_F32) launch_pdl(bit, clamped_glu_kernel<float>, grid, block, (size_t)0, stream, gu, (float*)mid, F, limit, alpha, shift, bias);
+  else if (out_dtype == DT_BF16) launch_pdl(bit, clamped_glu_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, gu, (__nv_bfloat16*)mid, F, limit, alpha, shift, bias);
   else EL_REFUSE(false, "clamped_glu: unknown dtype code %d", out_dtype);
   EL_LAUNCH_CHECK("clamped_glu");
   return 0;

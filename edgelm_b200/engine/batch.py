@@ -60,6 +60,7 @@ class StepContext:
         # models that carry several residual streams: the read that the running layer's last write should also do
         # ((in-weights, norm weight, eps, output, whether it is the next layer's input) or None), and the next layer's input if done
         self.streams_next = self.streams_h = None
+        self.rows_to_add = None        # rows that the next layer adds to the residual stream before anything else (or None)
         self.token_ids = self.tok_pos = self.tok_seq = self.seq_index = self.seq_pos = self.want_rows = None
         self.seq_tok0 = None           # packed row of each sequence's first token, then the token count (int32 [n_seqs + 1])
         self.seq_slots = None          # real slot of each sequence (int32 device tensor): state groups, sampler streams

@@ -34,6 +34,7 @@ class DecoderModel:
         self.carry = any(hasattr(l, "first_read") for l in self.layers)
         if self.carry != all(hasattr(l, "first_read") for l in self.layers) or (self.streams > 1 and not self.carry):
             raise ConfigError(f"a plan with {self.streams} residual streams needs layer arrangements that all carry them")
+        self.keeps_embedding = any(e.add_embedding for e in self.schedule)      # a copy of the embedding's output outlives the layers
         for i, e in enumerate(self.schedule):
             need = self.layers[e.layer].cache_need()
             if e.reads_cache_of is not None and need is not None and not getattr(self.layers[e.layer].mixer, "reads_foreign_cache", False):
@@ -50,7 +51,12 @@ class DecoderModel:
         return out
 
     def ignorable_weights(self):
-        return tuple(self.head.ignorable()) if hasattr(self.head, "ignorable") else ()
+        """Names that the files may hold without their being used (a tied model's copy of the head; a norm stored for a
+        sublayer that the layer does not have)."""
+        out = list(self.head.ignorable()) if hasattr(self.head, "ignorable") else []
+        for layer in self.layers:
+            out += list(layer.ignorable()) if hasattr(layer, "ignorable") else []
+        return tuple(out)
 
     def load(self, tensors, device):
         """Take the tensors (name -> tensor in the stored dtype); each part keeps what it computes with."""
@@ -85,7 +91,7 @@ class DecoderModel:
 
     def workspace_bytes(self, n_tokens, n_seqs, n_want):
         d = self.plan.hidden_size
-        x = nbytes((n_tokens, d), torch.float32)
+        x = nbytes((n_tokens, d), torch.float32) * (2 if self.keeps_embedding else 1)
         if self.carry:
             x += nbytes((n_tokens, self.streams, d), torch.float32) + nbytes((n_tokens, d), self.dtype)
         layers = max(l.workspace_bytes(n_tokens, n_seqs) for l in self.layers)
@@ -147,6 +153,10 @@ class DecoderModel:
         with ctx.prof("embedding"):
             self.embedding.forward(ctx, x)
         carried = x
+        x0 = None
+        if self.keeps_embedding:
+            x0 = ws.alloc((T, self.plan.hidden_size), torch.float32)
+            x0.copy_(x)
         if self.carry:
             # the layers carry `streams` copies of x; each layer's last write also does the read that follows it (the next
             # layer's first, into `h_next`; after the last layer the sum of the streams, into x)
@@ -162,6 +172,14 @@ class DecoderModel:
             ctx.weights_after = self.layers[nxt].first_weights() if nxt is not None else ()
             if self.carry:
                 ctx.streams_next = (*self.layers[nxt].first_read(), h_next, True) if nxt is not None else (self._ones, None, 0.0, x, False)
+            # (the embedding's output joining the stream again: the layer's first pass over x does it, if its arrangement
+            # can (`takes_added_rows`), else a pass of its own)
+            ctx.rows_to_add = x0 if e.add_embedding else None
+            if e.add_embedding and not getattr(self.layers[e.layer], "takes_added_rows", False):
+                from ..csrc import ops
+                with ctx.prof("add_embedding"):
+                    ops.scaled_sum(x0, 1.0, x0, 0.0, x, add=True)
+                ctx.rows_to_add = None
             self.layers[e.layer].forward(ctx, carried, entry)
         ctx.weights_after = ()
         if R:

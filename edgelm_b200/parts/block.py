@@ -1,6 +1,7 @@
 """Arrangements of one layer's parts.  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x))
 (adarsh-sgh/edgelm tools/elm.py:122-153); a layer may have no feed-forward.  "sublayer_norm": x += norm1(mixer(x)); x += norm2(ffn(x)), with an
-optional blend of the mixer's input with the previous token's.  "hyper": the pre-norm arrangement over several copies of the
+optional blend of the mixer's input with the previous token's.  "parallel_prenorm": x += mixer(norm1(x)) + ffn(norm2(x)), both
+sublayers reading the same x.  "hyper": the pre-norm arrangement over several copies of the
 residual stream, which every sublayer reads through learned weights and rewrites through a learned matrix."""
 import torch
 
@@ -87,6 +88,53 @@ class PreNormBlock(Part):
         if self.ffn is not None:
             with ctx.ws.frame():
                 self.ffn.forward(ctx, self._normed(ctx, x, self.ffn_norm, self.ffn), x)
+
+
+@register_block("parallel_prenorm")
+class ParallelPreNormBlock(PreNormBlock):
+    """Both sublayers read the same x: x += mixer(norm1(x)) + ffn(norm2(x)); a layer may have no feed-forward.  The two
+    norms divide by the same root mean square, so one kernel computes it once and writes both inputs (`rmsnorm_pair`); the
+    sublayers then add into x one after the other (their residual sums stay the epilogues of their last products).  Rows that
+    the model hands in as `ctx.rows_to_add` join x in that same first pass."""
+    takes_added_rows = True
+
+    def __init__(self, layer_spec, env):
+        super().__init__(layer_spec, env)
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not (getattr(n, "fusable", False) and n.eps == self.mixer_norm.eps):
+                raise ConfigError(f"block 'parallel_prenorm': the norm '{n.kind}' is not one that the paired kernel computes (weight, one eps)")
+
+        self.unused_norm = layer_spec.options.get("unused_norm") if self.ffn is None else None
+
+    def ignorable(self):
+        """A layer without a feed-forward may still come with its second norm's weight in the files."""
+        return (self.prefix + self.unused_norm,) if self.unused_norm else ()
+
+    def workspace_bytes(self, n_tokens, n_seqs):
+        inner = max(self.mixer.workspace_bytes(n_tokens, n_seqs), self.ffn.workspace_bytes(n_tokens, n_seqs) if self.ffn is not None else 0)
+        return 2 * nbytes((n_tokens, self.hidden), self.dtype) + inner
+
+    def describe(self):
+        ffn = f" + {self.ffn_norm.describe()} -> {self.ffn.describe()}" if self.ffn is not None else ""
+        return f"{self.kind}: x += {self.mixer_norm.describe()} -> {self.mixer.describe()}{ffn}"
+
+    def forward(self, ctx, x, cache):
+        T, ws = x.shape[0], ctx.ws
+        after_layer = ctx.weights_after
+        add, ctx.rows_to_add = ctx.rows_to_add, None
+        with ws.frame():
+            h1 = ws.alloc((T, self.hidden), self.dtype)
+            h2 = ws.alloc((T, self.hidden), self.dtype) if self.ffn is not None else None
+            with ctx.prof("norm_pair"):
+                ops.rmsnorm_pair(x, self.mixer_norm.weight, self.mixer_norm.eps, h1, self.ffn_norm.weight if self.ffn is not None else None, h2, add=add)
+            if self.ffn is not None:
+                ctx.weights_after = self.ffn.first_weights()
+            with ws.frame():
+                self.mixer.forward(ctx, h1, x, cache)
+            ctx.weights_after = after_layer
+            if self.ffn is not None:
+                with ws.frame():
+                    self.ffn.forward(ctx, h2, x)
 
 
 @register_block("sublayer_norm")

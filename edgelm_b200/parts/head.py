@@ -1,6 +1,7 @@
 """Output head: logits = norm(x[wanted rows]) H^T in float32, H the embedding table when tied
 (adarsh-sgh/edgelm tools/elm.py:154-160).  The final norm is applied by the model before this
-part; here is the matrix product alone."""
+part; here is the matrix product alone, and with `softcap` (a constant c of the spec) logits <- c tanh(logits / c) after it."""
+from ..csrc import ops
 from . import linear
 from .base import Part, as_matrix
 from .registry import register_head
@@ -11,11 +12,12 @@ class LMHead(Part):
     graph_safe = True
     def __init__(self, spec, env):
         self.vocab_size, self.dim, self.name, self.tied_to = spec["vocab_size"], spec["dim"], spec["name"], spec["tied_to"]
+        self.softcap = float(spec.get("softcap") or 0.0)
         self.dtype = env.dtype
         self.weight = None
 
     def sizes(self):
-        return {"vocab": self.vocab_size, "tied": bool(self.tied_to)}
+        return {"vocab": self.vocab_size, "tied": bool(self.tied_to), **({"logit_softcap": self.softcap} if self.softcap else {})}
 
     def flops(self, n_rows, attended=0):
         return 2.0 * n_rows * self.dim * self.vocab_size
@@ -32,3 +34,5 @@ class LMHead(Part):
 
     def forward(self, ctx, xn, logits):
         linear.matmul(ctx, xn, self.weight, logits)
+        if self.softcap:
+            ops.softcap(logits, self.softcap)

@@ -24,6 +24,9 @@ Options, each with its constants in the spec:
               own (q and k rows laid out head by head as [map 1, map 2]) and a softmax of its own over the same values.
               With lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + offset (four tensors of head_dim, one number per layer):
               o = a_1 - lambda a_2, divided by its root mean square over the head's values (eps), times (1 - offset)
+    head_gate True: one more projection of the mixer's input with one row per query head (`names["gate"]`, no bias); head h's
+              output is multiplied by the sigmoid of its number before the output projection.  The rows ride in the stacked
+              q, k, v product; the attention kernels multiply before they round.
 """
 import torch
 
@@ -104,6 +107,7 @@ class MaskedAttention(Part):
         self.out_bias = bool(spec.get("output_bias", self.bias))
         self.taps = int(spec.get("conv") or 0)                    # 0: no convolution
         self.qk_norm, self.diff = spec.get("qk_norm"), spec.get("diff")
+        self.head_gate = bool(spec.get("head_gate", False))
         self.maps = 2 if self.diff else 1
         self.names = dict(spec["names"])
         self.dtype = env.dtype
@@ -113,11 +117,14 @@ class MaskedAttention(Part):
             raise ConfigError(f"masked_attention: head sizes {self.dk} / {self.dv} are not taken (key rows to 1024, values to 512)")
         if self.diff and "sink" in self.names:
             raise ConfigError("masked_attention: differential maps take no sink")
+        if self.diff and self.head_gate:
+            raise ConfigError("masked_attention: differential maps take no gate per head")
         if self.rot % 2 or not 0 <= self.rot <= self.dk:
             raise ConfigError(f"masked_attention: {self.rot} rotated dimensions of a head of {self.dk}")
         self.mask, self.mask_size = read_mask(spec.get("mask"), "masked_attention")
         self.kw = self.dk * self.maps                                # what a head's queries and a key row hold
         self.d_qkv = (self.nh + self.nkv) * self.kw + self.nkv * self.dv
+        self.d_in = self.d_qkv + (self.nh if self.head_gate else 0)     # columns of the stacked product: q | k | v | gate
         self.tile_tokens = max(1, 32 // (self.nh // self.nkv))
         self.freq = self.b_qkv = self.b_o = self.sink = self.conv_w = self.q_norm = self.k_norm = self.no_tail = None
         self.lam = 0.0
@@ -134,10 +141,12 @@ class MaskedAttention(Part):
             out["diff_offset"] = float(self.diff["offset"])
         if self.qk_norm:
             out["qk_norm"] = True
+        if self.head_gate:
+            out["head_gate"] = True
         return out
 
     def flops(self, n_tokens, attended):
-        proj = 2.0 * n_tokens * self.hidden * (self.d_qkv + self.nh * self.dv)
+        proj = 2.0 * n_tokens * self.hidden * (self.d_in + self.nh * self.dv)
         if self.mask != ops.MASK_CAUSAL:
             attended = min(attended, n_tokens * self.mask_size)
         return proj + 2.0 * attended * self.nh * self.maps * (self.dk + self.dv)
@@ -147,6 +156,8 @@ class MaskedAttention(Part):
         rows = {"q": self.nh * self.kw, "k": self.nkv * self.kw, "v": self.nkv * self.dv}
         out = {prefix + n[k]: (r, self.hidden) for k, r in rows.items()}
         out[prefix + n["o"]] = (self.hidden, self.nh * self.dv)
+        if self.head_gate:
+            out[prefix + n["gate"]] = (self.nh, self.hidden)
         if self.bias:
             out.update({prefix + n[k] + n["bias"]: (r,) for k, r in rows.items()})
         if self.out_bias:
@@ -163,7 +174,8 @@ class MaskedAttention(Part):
 
     def load(self, tensors, prefix, device):
         n = self.names
-        self.w_qkv = torch.cat([as_matrix(tensors[prefix + n[k]], self.dtype, device) for k in ("q", "k", "v")], dim=0).contiguous()
+        stacked = ("q", "k", "v", "gate") if self.head_gate else ("q", "k", "v")
+        self.w_qkv = torch.cat([as_matrix(tensors[prefix + n[k]], self.dtype, device) for k in stacked], dim=0).contiguous()
         self.w_o = as_matrix(tensors[prefix + n["o"]], self.dtype, device)
         if self.bias:
             self.b_qkv = torch.cat([as_vector(tensors[prefix + n[k] + n["bias"]], device) for k in ("q", "k", "v")]).contiguous()
@@ -195,7 +207,7 @@ class MaskedAttention(Part):
 
     def workspace_bytes(self, n_tokens, n_seqs):
         f32 = torch.float32
-        return (nbytes((n_tokens, self.d_qkv), f32) * (2 if self.taps else 1) + nbytes((n_tokens, self.nh * self.kw), f32) +
+        return (nbytes((n_tokens, self.d_in), f32) + (nbytes((n_tokens, self.d_qkv), f32) if self.taps else 0) + nbytes((n_tokens, self.nh * self.kw), f32) +
                 nbytes((n_tokens, self.nh * self.maps * self.dv), f32 if self.diff else self.dtype) +
                 (nbytes((n_tokens, self.nh * self.dv), self.dtype) if self.diff else 0) + nbytes((n_tokens, self.hidden), self.dtype) +
                 splits_room(n_seqs, self.nh * self.maps, self.dv))
@@ -203,16 +215,18 @@ class MaskedAttention(Part):
     def forward(self, ctx, h, x, cache, accumulate=True):
         h = linear.as_tensor(h)
         T, ws = h.shape[0], ctx.ws
-        qkv = ws.alloc((T, self.d_qkv), torch.float32)
+        u = ws.alloc((T, self.d_in), torch.float32)
         with ctx.prof("qkv_proj"):
-            linear.matmul(ctx, h, self.w_qkv, qkv, prefetch=(self.w_o,))
+            linear.matmul(ctx, h, self.w_qkv, u, prefetch=(self.w_o,))
+        qkv = u[:, :self.d_qkv]
+        gate = u[:, self.d_qkv:] if self.head_gate else None
         bias = self.b_qkv
         if self.taps:
             conv = cache.get("conv") if self.taps > 1 else None
             cache = cache["kv"] if self.taps > 1 else cache
             mixed = ws.alloc((T, self.d_qkv), torch.float32)
             with ctx.prof("qkv_conv"):
-                ops.conv_act(qkv, 0, self.conv_w, None, conv.state if conv is not None else self.no_tail, mixed, ctx.tok_seq, ctx.seq_tok0,
+                ops.conv_act(u, 0, self.conv_w, None, conv.state if conv is not None else self.no_tail, mixed, ctx.tok_seq, ctx.seq_tok0,
                              ctx.seq_slots, ctx.n_seqs, update_state=True, in_bias=bias, act=None)
             qkv, bias = mixed, None
         q = ws.alloc((T, self.nh * self.kw), torch.float32)
@@ -228,15 +242,15 @@ class MaskedAttention(Part):
                 part = ws.alloc((T * self.nh * self.maps * splits * (2 + self.dv),), torch.float32) if splits > 1 else None
                 tseq, ttok0, tntok, tpos0 = single_token_tiles(ctx)
                 ops.masked_attn_tiled(q, a, cache.k, cache.v, table, tseq, ttok0, tntok, tpos0, T, 1, self.nh, self.nkv, self.dk, self.dv,
-                                      self.scale, self.mask, self.mask_size, self.sink, n_splits=splits, part=part, maps=self.maps)
+                                      self.scale, self.mask, self.mask_size, self.sink, n_splits=splits, part=part, maps=self.maps, gate=gate)
             elif ctx.all_single:
                 ops.masked_attn(q, a, cache.k, cache.v, ctx.tok_pos, ctx.tok_seq, table, self.nh, self.nkv, self.dk, self.dv, self.scale,
-                                self.mask, self.mask_size, self.sink, most_keys(self.mask, self.mask_size), maps=self.maps)
+                                self.mask, self.mask_size, self.sink, most_keys(self.mask, self.mask_size), maps=self.maps, gate=gate)
             else:
                 tiles = ctx.tiles(self.tile_tokens)
                 ops.masked_attn_tiled(q, a, cache.k, cache.v, table, tiles.seq, tiles.tok0, tiles.ntok, tiles.pos0, tiles.count,
                                       self.tile_tokens, self.nh, self.nkv, self.dk, self.dv, self.scale, self.mask, self.mask_size, self.sink,
-                                      maps=self.maps)
+                                      maps=self.maps, gate=gate)
         if self.diff:
             o = ws.alloc((T, self.nh * self.dv), self.dtype)
             with ctx.prof("diff_combine"):

@@ -68,8 +68,4 @@ class ParallelMixers(Part):
         with ws.frame():
             self.right.forward(ctx, h, y2, cache.get("right"), accumulate=False)
         with ctx.prof("parallel_sum"):
-            if accumulate:
-                ops.scaled_sum(y1, self.left_scale, y2, self.right_scale, y1)
-                x.add_(y1)
-            else:
-                ops.scaled_sum(y1, self.left_scale, y2, self.right_scale, x)
+            ops.scaled_sum(y1, self.left_scale, y2, self.right_scale, x, add=accumulate)

@@ -1,9 +1,14 @@
 """SwiGLU feed-forward: x += (silu(h Wg^T) * (h Wu^T)) Wd^T, silu(z) = z / (1 + exp(-z)), no bias
 (adarsh-sgh/edgelm src/kernels_ref.cpp:143-160, tools/elm.py:140-152).  Gate and up never reach
 memory: the activation is the epilogue of their matrix product, the residual sum that of the
-down projection."""
+down projection.  With `bias` (a suffix of the tensors' names) all three projections have biases: x += Wd (silu(Wg h + bg) *
+(Wu h + bu)) + bd.  Gate and up then run as one product over the two weights stacked, whose float32 sums feed the gated unit's
+kernel together with the biases; the down projection's bias is added to the residual stream after its product."""
+import torch
+
+from ..csrc import ops
 from . import linear
-from .base import Part, as_matrix, nbytes
+from .base import Part, as_matrix, as_vector, nbytes
 from .registry import register_ffn
 
 
@@ -15,38 +20,58 @@ class SwiGLU(Part):
     def __init__(self, spec, env):
         self.hidden, self.inter = spec["hidden_size"], spec["intermediate_size"]
         self.names = dict(spec["names"])
+        self.bias = spec.get("bias")            # a suffix, or None
         self.dtype = env.dtype
-        self.w_gate = self.w_up = self.w_down = None
+        self.w_gate = self.w_up = self.w_down = self.w_gu = self.b_gu = self.b_down = None
 
     def sizes(self):
-        return {"intermediate": self.inter}
+        return {"intermediate": self.inter, **({"ffn_bias": True} if self.bias else {})}
 
     def flops(self, n_tokens, attended):
         return 6.0 * n_tokens * self.hidden * self.inter
 
     def weight_shapes(self, prefix):
         n = self.names
-        return {prefix + n["gate"]: (self.inter, self.hidden), prefix + n["up"]: (self.inter, self.hidden),
-                prefix + n["down"]: (self.hidden, self.inter)}
+        out = {prefix + n["gate"]: (self.inter, self.hidden), prefix + n["up"]: (self.inter, self.hidden),
+               prefix + n["down"]: (self.hidden, self.inter)}
+        if self.bias:
+            out.update({prefix + n["gate"] + self.bias: (self.inter,), prefix + n["up"] + self.bias: (self.inter,),
+                        prefix + n["down"] + self.bias: (self.hidden,)})
+        return out
 
     def load(self, tensors, prefix, device):
         n = self.names
-        self.w_gate = as_matrix(tensors[prefix + n["gate"]], self.dtype, device)
-        self.w_up = as_matrix(tensors[prefix + n["up"]], self.dtype, device)
         self.w_down = as_matrix(tensors[prefix + n["down"]], self.dtype, device)
+        if self.bias:
+            self.w_gu = torch.cat([as_matrix(tensors[prefix + n[k]], self.dtype, device) for k in ("gate", "up")], dim=0).contiguous()
+            self.b_gu = torch.cat([as_vector(tensors[prefix + n[k] + self.bias], device) for k in ("gate", "up")]).contiguous()
+            self.b_down = as_vector(tensors[prefix + n["down"] + self.bias], device)
+        else:
+            self.w_gate = as_matrix(tensors[prefix + n["gate"]], self.dtype, device)
+            self.w_up = as_matrix(tensors[prefix + n["up"]], self.dtype, device)
 
     def workspace_bytes(self, n_tokens, n_seqs):
-        return nbytes((n_tokens, self.inter), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype)
+        return (nbytes((n_tokens, self.inter), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype) +
+                (nbytes((n_tokens, 2 * self.inter), torch.float32) if self.bias else 0))
 
     def first_weights(self):
-        return (self.w_gate, self.w_up)
+        return (self.w_gu,) if self.bias else (self.w_gate, self.w_up)
 
     def forward(self, ctx, h, x, accumulate=True):
         """x += feed_forward(h); with `accumulate` False, x = feed_forward(h) (float32), for an arrangement that
         norms the sublayer's output before the residual sum."""
         mid = ctx.ws.alloc((h.shape[0], self.inter), self.dtype)
-        with ctx.prof("gate_up_swiglu"):
-            linear.matmul(ctx, h, self.w_gate, mid, epilogue=linear.EPI_SWIGLU, w2=self.w_up, prefetch=(self.w_down,))
+        if self.bias:
+            gu = ctx.ws.alloc((h.shape[0], 2 * self.inter), torch.float32)
+            with ctx.prof("gate_up"):
+                linear.matmul(ctx, h, self.w_gu, gu, prefetch=(self.w_down,))
+            with ctx.prof("swiglu_bias"):
+                ops.clamped_glu(gu, mid, 0.0, 1.0, shift=0.0, bias=self.b_gu)
+        else:
+            with ctx.prof("gate_up_swiglu"):
+                linear.matmul(ctx, h, self.w_gate, mid, epilogue=linear.EPI_SWIGLU, w2=self.w_up, prefetch=(self.w_down,))
         with ctx.prof("down_proj_residual"):
             linear.matmul(ctx, mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL if accumulate else linear.EPI_STORE,
                           residual=x if accumulate else None, prefetch=ctx.weights_after)
+            if self.b_down is not None:
+                ops.add_row_bias(x, self.b_down)
