@@ -6,6 +6,7 @@
     python bench.py --design sagizen        # that design beside the Llama decoder at equal sizes (a line of its own shape)
     python bench.py --design vosulorn       # the same for the Vosulorn design
     python bench.py --design redenex        # the same for the Redenex design
+    python bench.py --design radupel        # the Radupel design beside the Sagizen design at equal sizes
 
 A "step" is one decode step of the whole batch.  The default run has the layer sizes of the
 SmolLM2-135M-shaped configuration with random weights N(0, 0.02), bfloat16, a batch of 8
@@ -263,7 +264,9 @@ def measure(preset, args, peaks, steps, warmup, batches, with_clocks):
 
 DESIGN_PAIRS = {"sagizen": [("sagizen-576", "smollm2-135m", 8), ("sagizen-2048", "smollm2-1.7b", 4)],
                 "vosulorn": [("vosulorn-576", "smollm2-135m", 8), ("vosulorn-2048", "smollm2-1.7b", 4)],
-                "redenex": [("redenex-576", "smollm2-135m", 8), ("redenex-2048", "smollm2-1.7b", 4)]}
+                "redenex": [("redenex-576", "smollm2-135m", 8), ("redenex-2048", "smollm2-1.7b", 4)],
+                # (the closest earlier model: the design whose layers also hold an attention beside a linear recurrence)
+                "radupel": [("radupel-576", "sagizen-576", 8), ("radupel-2048", "sagizen-2048", 4)]}
 
 
 def parts_profile(model, vocab, ctx, prompt_tokens=2048, batch=8):

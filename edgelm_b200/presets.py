@@ -53,7 +53,31 @@ def _redenex(vocab, width, ff, pattern, rec_width, rec_blocks, heads, kv_heads, 
             "streams": streams, "max_positions": 8192, "layers": [rec if c == "r" else att for c in pattern]}
 
 
+def _radupel(vocab, width, ff, pattern, loop, heads, kv_heads, lin_heads, experts, expert_ff, shared_ff):
+    """A Radupel-shaped model: every layer a softmax attention (heads of 64, half of each rotated, a convolution of 4 taps on
+    q, k and v, a gate per head) beside a linear attention with a constant decay per head (heads of 64 x 64), with a dense
+    feed-forward ("d") or a mixture of `experts` clamped experts plus two identity experts in two groups, two chosen of the
+    better group, and a shared expert ("m"), in the order of `pattern`; `loop` (start, stop, times) or None."""
+    decay = [round(1.0 - 2.0 ** -(3.0 + 6.0 * h / max(1, lin_heads - 1)), 6) for h in range(lin_heads)]
+    mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "conv": 4, "scale": 0.125,
+                      "rot": {"base": 250000.0, "dims": 32}},
+             "left_scale": 1.0, "right": {"heads": lin_heads, "dim": 64, "vdim": 64, "decay": decay}, "right_scale": 1.0}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
+           "router": {"experts": experts, "top": 2, "identity": 2, "groups": {"count": 2, "keep": 1}, "scale": 2.5},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    out = {"architecture": "Radupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "max_positions": 8192,
+           "layers": [{"type": "parallel", "mixer": mixer, "mlp": dense if c == "d" else moe} for c in pattern]}
+    if loop:
+        out["loop"] = dict(zip(("start", "stop", "times"), loop))
+    return out
+
+
 PRESETS = {
+    # the layer sizes of smollm2-135m and smollm2-1.7b (width, feed-forward, as many query, key and output rows, vocabulary)
+    # in the Radupel design: dense and expert feed-forwards in turn, the first layers run twice (8 and 4 layer runs)
+    "radupel-576": _radupel(49152, 576, 1536, "dmdmdm", (0, 2, 2), 9, 3, 9, 8, 768, 768),
+    "radupel-2048": _radupel(49152, 2048, 8192, "dmd", (0, 1, 2), 32, 32, 32, 8, 4096, 4096),
     # the layer sizes of smollm2-135m and smollm2-1.7b (width, feed-forward, as many query, key and output rows, vocabulary)
     # in the Redenex design: two recurrent layers to one of attention, four residual streams
     "redenex-576": _redenex(49152, 576, 1536, "rrarrarr", 768, 12, 9, 3, 32, 1024, 4),

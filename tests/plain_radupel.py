@@ -187,3 +187,14 @@ def forward(cfg, w, tokens, return_layers=False):
     if cap:
         logits = cap * np.tanh(logits / cap)
     return (logits, np.stack(runs)) if return_layers else logits
+
+
+def load(model_dir):
+    """(config.json dictionary, name -> float64 array) of a model folder."""
+    import json
+    import os
+
+    from plain_redenex import read_safetensors
+    with open(os.path.join(model_dir, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, read_safetensors(os.path.join(model_dir, "model.safetensors"))

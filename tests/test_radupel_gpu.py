@@ -1,0 +1,260 @@
+"""The Radupel decoder through the engine against the plain implementation (tests/plain_radupel.py), in float32 and
+bfloat16, cut in every way the engine allows: whole prompts, a long tail decoded token by token, pieces down to one and
+two tokens, unequal batches on slots and pages that are used again, steps cut by the engine itself, greedy generation
+through the package's entry point, the command line and the trace replay.  Three configurations that differ in every size
+(tests/radupel_models.py), and models whose weights make one far key, or a state left hundreds of tokens ago, decide the
+logits."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import helpers as H
+import plain_radupel as plain
+import radupel_models as M
+
+pytestmark = pytest.mark.gpu
+
+NAMES = ["a", "b", "c"]
+DTYPES = ["float32", "bfloat16"]
+TOL = {"float32": 5e-5}
+# bfloat16: a router's close call decides a token's experts and the group they come from, and the rounding of the router's
+# input moves close calls, so single rows may be far off (the float32 runs hold every row); the typical row must be close and
+# nine rows in ten near.  A kernel that read or wrote the wrong thing in bfloat16 would move most rows by the logits' own size.
+BF16_TYPICAL, BF16_MOST, BF16_WORST = 8e-2, 0.35, 0.6
+
+
+@pytest.fixture(scope="module")
+def dirs(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("radupel")
+    return {n: M.write_dir(str(tmp / n), M.CONFIGS[n], seed=51 + i, negative_corrections=n in M.NEGATIVE_CORRECTIONS) for i, n in enumerate(NAMES)}
+
+
+class Oracle:
+    def __init__(self, d):
+        self.cfg, self.W = plain.load(d)
+        self.memo = {}
+
+    def logits(self, toks):
+        key = tuple(toks)
+        if key not in self.memo:
+            self.memo[key] = plain.forward(self.cfg, self.W, list(toks))
+        return self.memo[key]
+
+
+@pytest.fixture(scope="module")
+def oracles(dirs):
+    return {n: Oracle(d) for n, d in dirs.items()}
+
+
+_engines = {}
+
+
+def engine_for(dirs, name, dtype, max_tokens=1536, **kw):
+    from edgelm_b200.engine.engine import Engine
+    key = (dirs[name], dtype, max_tokens, tuple(sorted(kw.items())))
+    if key not in _engines:
+        _engines[key] = Engine.from_dir(dirs[name], dtype=dtype, max_tokens=max_tokens, **kw)
+    return _engines[key]
+
+
+def close(got, want, dtype, what=""):
+    err = H.rel_err(got, want)
+    if dtype == "bfloat16":
+        rows = np.abs(np.asarray(got, np.float64) - want).max(-1) / max(1.0, np.abs(want).max())
+        if len(rows) < 8:
+            assert np.median(rows) < BF16_MOST, (what, err)
+        else:
+            assert np.median(rows) < BF16_TYPICAL and np.quantile(rows, 0.9) < BF16_MOST, (what, err, float(np.median(rows)), float(np.quantile(rows, 0.9)))
+        return
+    assert err < TOL[dtype], (what, err)
+    share, n = H.decisive_agreement(got, want, gap=0.01)
+    assert share == 1.0, (what, share, n)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_prompts(dirs, oracles, name, dtype):
+    """Lengths around everything that has an edge: one token, two, the convolutions' taps, a page of 64, several pages."""
+    eng = engine_for(dirs, name, dtype)
+    for i, n in enumerate((1, 2, 3, 4, 5, 8, 31, 32, 33, 63, 64, 65, 127, 128, 129, 200)):
+        toks = M.tokens(M.CONFIGS[name], n, i)
+        close(H.run_whole(eng, toks), oracles[name].logits(toks), dtype, n)
+    eng.cache.check()
+    eng.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_prompt_then_long_decoding(dirs, oracles, name, dtype):
+    """A prompt in one step and 150 tokens one by one: the linear attention's states and the convolutions' tails of every
+    pass of a looped layer are carried, over page borders; and from the very first token on."""
+    eng = engine_for(dirs, name, dtype)
+    toks = M.tokens(M.CONFIGS[name], 215, 20)
+    close(H.run_tail_one_by_one(eng, toks, 150), oracles[name].logits(toks), dtype, "tail 150")
+    toks = M.tokens(M.CONFIGS[name], 80, 21)
+    close(H.run_tail_one_by_one(eng, toks, 79), oracles[name].logits(toks), dtype, "all but one decoded")
+    toks = M.tokens(M.CONFIGS[name], 72, 22)
+    close(H.run_tail_one_by_one(eng, toks, 72), oracles[name].logits(toks), dtype, "all decoded")
+    eng.cache.check()
+    eng.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_pieces_of_a_prompt(dirs, oracles, name, dtype):
+    """One stream in pieces of many sizes, down to one and two tokens (shorter than a convolution's tail), with cuts inside
+    pages and at their edges."""
+    from edgelm_b200.engine.engine import StepEntry
+    eng = engine_for(dirs, name, dtype)
+    toks = M.tokens(M.CONFIGS[name], 230, 30)
+    want = oracles[name].logits(toks)
+    for cuts in ((2, 3, 64, 1, 37, 2, 2, 1, 70, 48), (1, 1, 2, 60, 66, 100), (129, 2, 99), (64, 64, 2, 100)):
+        assert sum(cuts) == len(toks)
+        slot = eng.open(1)[0]
+        rows, at = [], 0
+        for c in cuts:
+            rows.append(eng.step([StepEntry(slot, toks[at:at + c], list(range(c)))]).cpu().numpy())
+            at += c
+        eng.close([slot])
+        close(np.concatenate(rows, 0), want, dtype, cuts)
+    eng.cache.check()
+    eng.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_on_reused_slots(dirs, oracles, name, dtype):
+    """Requests of unequal lengths in batches of three, decoded together; shorter ones leave earlier; the next batch
+    takes the slots and pages just given back (states and tails must start from zero again).  Every request's logits
+    equal those it has alone."""
+    eng = engine_for(dirs, name, dtype, max_tokens=768)
+    cfg = M.CONFIGS[name]
+    requests = [M.tokens(cfg, n, 40 + i) for i, n in enumerate((150, 31, 1, 97, 64, 140, 2, 75, 66))]
+    got = H.run_batches(eng, requests, batch_size=3, decode_tail=25)
+    for r, g in zip(requests, got):
+        close(g, oracles[name].logits(r), dtype, len(r))
+    got = H.run_batches(eng, requests[::-1], batch_size=4, decode_tail=3)
+    for r, g in zip(requests[::-1], got):
+        close(g, oracles[name].logits(r), dtype, len(r))
+    eng.check_device_errors()
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_steps_cut_by_the_engine(dirs, oracles, name):
+    """An engine that runs at most 64 tokens at a time cuts a step of three prompts into consecutive smaller ones."""
+    from edgelm_b200.engine.engine import StepEntry
+    eng = engine_for(dirs, name, "float32", max_tokens=768, max_step_tokens=64)
+    cfg = M.CONFIGS[name]
+    requests = [M.tokens(cfg, n, 60 + i) for i, n in enumerate((150, 70, 33))]
+    slots = eng.open(3)
+    lg = eng.step([StepEntry(s, r, list(range(len(r)))) for s, r in zip(slots, requests)]).cpu().numpy()
+    eng.close(slots)
+    at = 0
+    for r in requests:
+        close(lg[at:at + len(r)], oracles[name].logits(r), "float32", len(r))
+        at += len(r)
+    eng.cache.check()
+    eng.check_device_errors()
+
+
+def test_a_far_key_decides(tmp_path):
+    """Softmax attention whose score scale is raised so that most tokens' softmax rests on one key, often hundreds of tokens
+    back, with the linear attention's share turned down: a key lost at a page border, a tail of the convolution dropped
+    between steps or a rotation by the wrong position moves the logits by their own size, in prompts and in decoding."""
+    from edgelm_b200.engine.engine import Engine
+    cfg = {"architecture": "Radupel", "vocab": 120, "width": 48, "norm": {"eps": 1e-5}, "loop": {"start": 1, "stop": 2, "times": 2}, "layers": [
+        M.layer(M.left(8, 1, 16, 16, 2, {"base": 5000.0, "dims": 8}, 5.0), M.right(1, 8, 8, (0.5,)), 1.5, 0.1, None),    # (eight heads to a key head)
+        M.layer(M.left(4, 2, 12, 20, 3, {"base": 200.0, "dims": 12}, 6.0), M.right(2, 8, 8, (0.5, 0.9)), 1.5, 0.1, M.dense(40)),
+        M.layer(M.left(2, 2, 8, 8, None, None, 8.0), M.right(1, 16, 8, (0.8,)), 1.5, 0.1, None)]}
+    d = M.write_dir(str(tmp_path / "far"), cfg, 77)
+    pcfg, PW = plain.load(d)
+    eng = Engine.from_dir(d, dtype="float32", max_tokens=1024)
+    toks = M.tokens(cfg, 300, 5)
+    want = plain.forward(pcfg, PW, toks)
+    # scores twenty times the usual size carry twenty times the rounding error into the exponentials: the tolerance is
+    # wider than elsewhere, and still a thousand times under what a lost key costs
+    assert np.abs(want).max() > 1.0
+    assert H.rel_err(H.run_whole(eng, toks), want) < 1e-3
+    assert H.rel_err(H.run_tail_one_by_one(eng, toks, 110), want) < 1e-3
+    eng.cache.check()
+    eng.check_device_errors()
+
+
+def test_a_state_left_long_ago_decides(tmp_path):
+    """Linear attention with decays of 0.999 and 1 and the softmax attention's share turned down: what the state took in
+    hundreds of tokens ago is most of it.  Decoding, pieces and a slot used again must carry it, and start it from zero,
+    exactly."""
+    from edgelm_b200.engine.engine import Engine, StepEntry
+    cfg = {"architecture": "Radupel", "vocab": 90, "width": 40, "norm": {"eps": 1e-6}, "loop": {"start": 0, "stop": 2, "times": 2}, "layers": [
+        M.layer(M.left(2, 1, 8, 8, 2, None, 0.3), M.right(2, 24, 12, (0.999, 1.0)), 0.1, 1.5, None),
+        M.layer(M.left(1, 1, 8, 8, None, None, 0.3), M.right(3, 8, 40, (1.0, 0.995, 0.999)), 0.1, 1.5, M.dense(24))]}
+    d = M.write_dir(str(tmp_path / "slow"), cfg, 9)
+    pcfg, PW = plain.load(d)
+    eng = Engine.from_dir(d, dtype="float32", max_tokens=1024)
+    toks = M.tokens(cfg, 260, 6)
+    want = plain.forward(pcfg, PW, toks)
+    # the state matters: the same last 60 tokens after another beginning give other logits
+    other = plain.forward(pcfg, PW, M.tokens(cfg, 200, 7) + toks[200:])
+    assert np.abs(other[-1] - want[-1]).max() > 0.05
+    assert H.rel_err(H.run_whole(eng, toks), want) < TOL["float32"]
+    assert H.rel_err(H.run_tail_one_by_one(eng, toks, 140), want) < TOL["float32"]
+    slot = eng.open(1)[0]
+    rows, at = [], 0
+    for c in (1, 2, 1, 60, 3, 130, 63):
+        rows.append(eng.step([StepEntry(slot, toks[at:at + c], list(range(c)))]).cpu().numpy())
+        at += c
+    eng.close([slot])
+    assert H.rel_err(np.concatenate(rows, 0), want) < TOL["float32"]
+    assert H.rel_err(H.run_whole(eng, toks[:50]), want[:50]) < TOL["float32"]       # the slot just given back starts from zero
+    eng.cache.check()
+    eng.check_device_errors()
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_greedy_generation_through_the_entry_point(dirs, oracles, name):
+    """`edgelm_b200.generate`: the generation loop, its batches, the sampler and the captured decode graphs."""
+    import edgelm_b200
+    cfg = M.CONFIGS[name]
+    prompts = [M.tokens(cfg, n, 80 + i) for i, n in enumerate((9, 1, 70, 30, 3))]
+    got = edgelm_b200.generate(dirs[name], prompts, n=24, dtype="float32", ctx=128, slots=3, stop=[], ignore_eos=True)
+    o = oracles[name]
+    for p, g in zip(prompts, got):
+        seq = list(p)
+        for t in g:     # the library's choice is the plain implementation's, or as good as it within float32 rounding
+            lg = plain.forward(o.cfg, o.W, seq)[-1]
+            assert lg[t] >= lg.max() - 1e-3, (len(p), len(seq))
+            seq.append(t)
+        assert len(g) == 24
+
+
+def test_info_and_trace_replay_commands(dirs, tmp_path):
+    """The command line describes the model from its parts, and bin/trace_run replays a trace of it."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-m", "edgelm_b200", "info", "-m", dirs["a"]], cwd=root, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert "decay_linear_attention" in out.stdout and "masked_attention" in out.stdout and "moe" in out.stdout and "parallel_prenorm" in out.stdout
+    cfg = M.CONFIGS["a"]
+    ra, rb = M.tokens(cfg, 70, 90), M.tokens(cfg, 9, 91)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": ra[:60], "want": [0, 59]}, {"id": "y", "tokens": rb[:8], "want": [7]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": [ra[60]], "want": [0]}, {"id": "y", "tokens": [rb[8]], "want": [0]}], "end": ["y"]}]
+    steps += [{"step": 2 + i, "entries": [{"id": "x", "tokens": [ra[61 + i]], "want": [0] if i % 2 else []}], "end": ["x"] if i == 8 else []} for i in range(9)]
+    for dtype in ("float32", "bfloat16"):
+        outdir = tmp_path / ("out_" + dtype)
+        run = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", dirs["a"], "--dtype", dtype, "--out", str(outdir), "--max-tokens", "256"],
+                             input="\n".join(json.dumps(s) for s in steps) + "\n", cwd=root, capture_output=True, text=True, timeout=600)
+        assert run.returncode == 0, run.stderr
+        assert [l for l in run.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(11)]
+        pcfg, W = plain.load(dirs["a"])
+        wa, wb = plain.forward(pcfg, W, ra), plain.forward(pcfg, W, rb)
+        tol = TOL["float32"] if dtype == "float32" else BF16_WORST
+        s0 = np.fromfile(outdir / "0.f32", dtype="<f4").reshape(3, -1)
+        assert H.rel_err(s0, np.stack([wa[0], wa[59], wb[7]])) < tol
+        s1 = np.fromfile(outdir / "1.f32", dtype="<f4").reshape(2, -1)
+        assert H.rel_err(s1, np.stack([wa[60], wb[8]])) < tol
+        assert not (outdir / "2.f32").exists()
+        s3 = np.fromfile(outdir / "3.f32", dtype="<f4").reshape(1, -1)
+        assert H.rel_err(s3, wa[62:63]) < tol
