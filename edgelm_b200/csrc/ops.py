@@ -1050,6 +1050,49 @@ def decay_scan(u, q_off, k_off, v_off, decay, state, o, seq_tok0, seq_slot, n_se
                                    int(n_seqs), int(heads), int(k_dim), int(v_dim), T, _stream()))
 
 
+DECAY_CHUNK = 64        # tokens of a chunk of the chunked form (LC in linear_attention.cu)
+
+
+def decay_chunked_takes(k_dim, v_dim):
+    """Whether the chunked form takes heads of k_dim x v_dim (its tiles must fit in shared memory)."""
+    c = DECAY_CHUNK     # (the rule of `edgelm_decay_chunked_takes`, answered without the library: plans are made on hosts without a device too)
+    smem = 4 * (2 * c * (k_dim + 1) + c * (v_dim + 1) + k_dim * (v_dim + 1) + c * (c + 1) + c + 1)
+    return 1 <= k_dim <= 128 and 1 <= v_dim <= 128 and smem <= 200 * 1024
+
+
+def decay_chunked_scratch_floats(n_tiles, heads, k_dim, v_dim):
+    return int(n_tiles) * heads * k_dim * v_dim
+
+
+def decay_powers(decay):
+    """The table of the chunked form: decay_h^0 .. decay_h^DECAY_CHUNK for every head, computed in float64 and rounded once
+    (float32 [heads, DECAY_CHUNK + 1], on the CPU; the caller moves it to the device)."""
+    d = torch.as_tensor(decay, dtype=torch.float64).reshape(-1, 1)
+    return (d ** torch.arange(DECAY_CHUNK + 1, dtype=torch.float64).reshape(1, -1)).to(torch.float32).contiguous()
+
+
+def decay_chunked(u, q_off, k_off, v_off, powers, state, o, seq_tok0, seq_slot, n_seqs, tile_tok0, tile_ntok, n_tiles, heads, k_dim, v_dim,
+                  act="silu", scratch=None):
+    """`decay_scan` for prompt steps, chunk by chunk (three launches): the step's tokens come as tiles of at most DECAY_CHUNK
+    consecutive tokens of one sequence, in the sequences' order, each sequence cut from its first row of the step.  `powers`:
+    the table of `decay_powers` on the device.  `act`:
+    "silu" (q, k, v pass it as they are read) or None.  `scratch`: float32 room for `decay_chunked_scratch_floats` values."""
+    _f32(powers, "powers"); _f32(state, "state"); _f32(o, "o")
+    for t, n in ((seq_tok0, "seq_tok0"), (seq_slot, "seq_slot"), (tile_tok0, "tile_tok0"), (tile_ntok, "tile_ntok")):
+        _i32(t, n)
+    T = u.shape[0]
+    _need(u.dtype == torch.float32 and u.is_cuda and u.stride(1) == 1, "decay_chunked: u must be float32 rows")
+    _need(max(q_off, k_off) + heads * k_dim <= u.shape[1] and v_off + heads * v_dim <= u.shape[1] and o.shape == (T, heads * v_dim), "decay_chunked: shapes")
+    _need(tuple(powers.shape) == (heads, DECAY_CHUNK + 1) and tuple(state.shape[1:]) == (heads, v_dim, k_dim) and act in ("silu", None), "decay_chunked: powers, state or activation")
+    need = decay_chunked_scratch_floats(n_tiles, heads, k_dim, v_dim)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=u.device)
+    _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need, "decay_chunked: scratch too small")
+    _check(lib().edgelm_decay_chunked(_p(u), u.stride(0), int(q_off), int(k_off), int(v_off), _p(powers), _p(state), _p(o), _p(seq_tok0), _p(seq_slot),
+                                      int(n_seqs), _p(tile_tok0), _p(tile_ntok), int(n_tiles), int(heads), int(k_dim), int(v_dim), 1 if act == "silu" else 0,
+                                      _p(scratch), _stream()), launches=3)
+
+
 def rmsnorm_pair(x, w1, eps, y1, w2=None, y2=None, add=None):
     """y1 = norm(x) * w1 and y2 = norm(x) * w2 with the rows' statistics computed once; with `add` [T, D] float32, x += add first
     (written back).  x float32 [T, D]; y1, y2 in the compute dtype."""

@@ -9,6 +9,11 @@ so the read-out sees the token's own write.  The heads side by side are divided 
 inside the root) and multiplied by a weight (`names["norm"]`), then by sigmoid(W_g h), and projected back.  A sequence's state
 is S per head.  The recurrence, its state and the norm are float32 in both precisions; the projections run in the compute
 dtype and their float32 sums are kept (one stacked product: q | k | v | gate).
+
+Steps of one token a sequence (and head sizes over 128) walk the tokens in order (`decay_scan`); prompt steps run the same
+recurrence chunk by chunk (`decay_chunked`: a chunk's own tokens as a small masked attention with the decay's powers as
+weights, what came before through the state at the chunk's start), which keeps the whole device busy where the walk has one
+warp per value channel.
 """
 import torch
 
@@ -59,17 +64,26 @@ class DecayLinearAttention(Part):
         self.norm_w = as_vector(tensors[prefix + n["norm"]], device)
         self.w_o = as_matrix(tensors[prefix + n["o"]], self.dtype, device)
         self.decay = torch.tensor(self.decay_values, dtype=torch.float64).to(device=device, dtype=torch.float32).contiguous()
+        self.powers = ops.decay_powers(self.decay_values).to(device)
 
     def first_weights(self):
         return (self.w_in,)
+
+    def _chunked(self):
+        return ops.decay_chunked_takes(self.d, self.e)
+
+    def tile_sizes(self):
+        return (ops.DECAY_CHUNK,) if self._chunked() else ()
 
     def cache_need(self):
         return StateNeed((self.heads, self.e, self.d))
 
     def workspace_bytes(self, n_tokens, n_seqs):
         f32 = torch.float32
+        chunks = n_tokens // ops.DECAY_CHUNK + n_seqs
         return (nbytes((n_tokens, self.d_in), f32) + nbytes((n_tokens, self.inner), f32) + nbytes((n_tokens, self.inner), self.dtype) +
-                nbytes((n_tokens, self.hidden), self.dtype))
+                nbytes((n_tokens, self.hidden), self.dtype) +
+                (nbytes((ops.decay_chunked_scratch_floats(chunks, self.heads, self.d, self.e),), f32) if self._chunked() else 0))
 
     def forward(self, ctx, h, x, cache, accumulate=True):
         h = linear.as_tensor(h)
@@ -77,13 +91,21 @@ class DecayLinearAttention(Part):
         u = ws.alloc((T, self.d_in), f32)
         with ctx.prof("linear_attn_in_proj"):
             linear.matmul(ctx, h, self.w_in, u, prefetch=(self.w_o,))
-        if self.act == "silu":
-            with ctx.prof("linear_attn_act"):
-                ops.silu_columns(u, 0, self.g_off)
         o = ws.alloc((T, self.inner), f32)
-        with ctx.prof("linear_attn_scan"):
-            ops.decay_scan(u, 0, self.k_off, self.v_off, self.decay, cache.state, o, ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs,
-                           self.heads, self.d, self.e)
+        if not ctx.all_single and T >= 8 * ctx.n_seqs and self._chunked():
+            tiles = ctx.tiles(ops.DECAY_CHUNK)
+            scratch = ws.alloc((ops.decay_chunked_scratch_floats(tiles.count, self.heads, self.d, self.e),), f32)
+            with ctx.prof("linear_attn_chunks"):
+                ops.decay_chunked(u, 0, self.k_off, self.v_off, self.powers, cache.state, o, ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs,
+                                  tiles.tok0, tiles.ntok, tiles.count, self.heads, self.d, self.e,
+                                  act="silu" if self.act == "silu" else None, scratch=scratch)
+        else:
+            if self.act == "silu":
+                with ctx.prof("linear_attn_act"):
+                    ops.silu_columns(u, 0, self.g_off)
+            with ctx.prof("linear_attn_scan"):
+                ops.decay_scan(u, 0, self.k_off, self.v_off, self.decay, cache.state, o, ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs,
+                               self.heads, self.d, self.e)
         on = ws.alloc((T, self.inner), self.dtype)
         with ctx.prof("linear_attn_gate_norm"):
             ops.gated_group_norm(o, u[:, self.g_off:], self.norm_w, on, 1, self.eps, gate_first=False, gate_act="sigmoid")

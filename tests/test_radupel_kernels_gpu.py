@@ -55,6 +55,53 @@ def test_decayed_linear_attention_over_steps(H, d, e, decay):
     assert torch.isnan(state[1]).all()
 
 
+@pytest.mark.parametrize("H,d,e,decay", [(2, 24, 16, (0.9, 0.999)), (3, 40, 8, (0.3, 0.97, 1.0)), (1, 32, 48, (0.95,)), (4, 8, 8, (0.5, 0.8, 0.99, 0.0)),
+                                         (2, 64, 64, (0.98, 0.93)), (1, 72, 128, (0.97,)), (2, 128, 5, (0.9, 0.6)), (1, 1, 1, (0.99,))])
+def test_decayed_linear_attention_chunk_by_chunk(H, d, e, decay):
+    """The same recurrence in its chunked form, which prompt steps take: pieces that end inside a chunk, at a chunk's edge and
+    one token past it, several sequences in a step, state rows in no particular order; then the walk goes on from the state
+    that the chunks left (decoding after a prompt), and the chunks from the walk's."""
+    g = np.random.default_rng(d * 3 + e)
+    total, cuts, slots = [300, 64, 131, 9], [[63, 1, 130, 1, 105], [64], [65, 2, 64], [2, 7]], [4, 0, 2, 5]
+    walked = [{1, 3}, set(), {1}, set()]                            # (sequence -> the steps of it that the walk takes instead)
+    C = 2 * H * d + H * e
+    raw = [torch.tensor(g.normal(size=(n, C + 3)), dtype=torch.float32).double().numpy() for n in total]
+    want = []
+    for s, n in enumerate(total):
+        x = plain.silu(raw[s][:, :C])
+        want.append(plain.decayed_linear_attention(x[:, :H * d].reshape(n, H, d), x[:, H * d:2 * H * d].reshape(n, H, d), x[:, 2 * H * d:].reshape(n, H, e),
+                                                   np.asarray(decay)).reshape(n, H * e))
+    assert ops.decay_chunked_takes(d, e)
+    state = torch.zeros(7, H, e, d, device=DEV)
+    state[1].fill_(float("nan"))
+    got = [np.zeros_like(w) for w in want]
+    for k, step in enumerate(steps_of(total, cuts)):
+        for walk in (False, True):
+            live = [(s, a, n) for s, (a, n) in enumerate(step) if n and ((k in walked[s]) == walk)]
+            if not live:
+                continue
+            lengths = [n for _, _, n in live]
+            tok0, _ = packed(lengths)
+            seqslot = i32([slots[s] for s, _, _ in live])
+            u = f32(np.concatenate([raw[s][a:a + n] for s, a, n in live]))
+            o = torch.full((u.shape[0], H * e), float("nan"), device=DEV)
+            if walk:
+                ops.silu_columns(u, 0, C)
+                ops.decay_scan(u, 0, H * d, 2 * H * d, f32(decay), state, o, tok0, seqslot, len(live), H, d, e)
+            else:
+                _, ttok0, tntok, _, count = make_tiles(lengths, [0] * len(live), ops.DECAY_CHUNK)
+                scratch = torch.full((ops.decay_chunked_scratch_floats(count, H, d, e),), float("nan"), device=DEV)
+                ops.decay_chunked(u, 0, H * d, 2 * H * d, ops.decay_powers(decay).to(DEV), state, o, tok0, seqslot, len(live), ttok0, tntok, count, H, d, e, act="silu", scratch=scratch)
+            o = o.cpu().numpy()
+            at = 0
+            for s, a, n in live:
+                got[s][a:a + n] = o[at:at + n]
+                at += n
+    for w, o in zip(want, got):
+        assert np.abs(o - w).max() < 2e-5 * max(1.0, np.abs(w).max())
+    assert torch.isnan(state[1]).all()
+
+
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_norm_over_all_heads_with_a_sigmoid_gate(out_dtype):
     g = np.random.default_rng(3)
