@@ -42,6 +42,7 @@ struct RopeAppend {
   // the gated epilogue's form (the struct travels to every kernel, so its constants ride along): out = g sigmoid(alpha g) v with
   // g = min(gate, limit), v = clamp(up, -limit, limit) + shift; limit 0: no clamps (alpha 1, shift 0: SwiGLU)
   float glu_limit = 0.f, glu_alpha = 1.f, glu_shift = 0.f;
+  const float* glu_bias = nullptr;   // [2 N] float32 (gate's | up's), added to the two sums before the unit; null: none
 };
 
 // Grouped products (a feed-forward of experts): the rows of `a` come grouped, every group's rows starting at a multiple of
@@ -124,8 +125,15 @@ __device__ __forceinline__ void epilogue_piece(const uint32_t* r, const uint32_t
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float acc = __uint_as_float(r[j0 + j]);
-      if (EPI == TC_EPI_SWIGLU) v[j] = glu_tc(acc, __uint_as_float(r2[j0 + j]), form.glu_limit, form.glu_alpha, form.glu_shift);
-      else v[j] = acc;
+      if (EPI == TC_EPI_SWIGLU) {
+        float g = acc, u = __uint_as_float(r2[j0 + j]);
+        if (form.glu_bias != nullptr) {     // (every thread of a tile asks for the same 2 x 32 values: they come out of L1)
+          const int c = min(col0 + j0 + j, N - 1);
+          g += form.glu_bias[c];
+          u += form.glu_bias[N + c];
+        }
+        v[j] = glu_tc(g, u, form.glu_limit, form.glu_alpha, form.glu_shift);
+      } else v[j] = acc;
     }
     if (full) {
       if (EPI == TC_EPI_RESIDUAL) {
@@ -426,7 +434,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // out = epilogue(sum over the splits, in their order, of the raw sums a split-K launch left).
 template <int EPI, typename TOut>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, TOut* out, int ldo, const float* residual,
-                                     int M, int N, float glu_limit, float glu_alpha, float glu_shift) {
+                                     int M, int N, float glu_limit, float glu_alpha, float glu_shift, const float* __restrict__ glu_bias) {
   constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
   const size_t plane = (size_t)M * N;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < plane; i += (size_t)gridDim.x * blockDim.x) {
@@ -437,7 +445,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     }
     const int m = (int)(i / N), n = (int)(i - (size_t)m * N);
     const size_t o = (size_t)m * ldo + n;
-    if (EPI == TC_EPI_SWIGLU) out[o] = from_f32<TOut>(glu_tc(a, b, glu_limit, glu_alpha, glu_shift));
+    if (EPI == TC_EPI_SWIGLU) out[o] = from_f32<TOut>(glu_tc(a + (glu_bias ? glu_bias[n] : 0.f), b + (glu_bias ? glu_bias[N + n] : 0.f), glu_limit, glu_alpha, glu_shift));
     else if (EPI == TC_EPI_RESIDUAL) out[o] = from_f32<TOut>(residual[o] + a);
     else out[o] = from_f32<TOut>(a);
   }
@@ -698,7 +706,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   if (EPI != TC_EPI_ROPE && splits > 1) {
     const size_t plane = (size_t)M * N;
     const int blocks = (int)((plane + 255) / 256 < 1184 ? (plane + 255) / 256 : 1184);
-    splitk_reduce_kernel<EPI, TOut><<<blocks, 256, 0, stream>>>(g_splitk_ws, splits, (TOut*)out, ldo, residual, M, N, rope.glu_limit, rope.glu_alpha, rope.glu_shift);
+    splitk_reduce_kernel<EPI, TOut><<<blocks, 256, 0, stream>>>(g_splitk_ws, splits, (TOut*)out, ldo, residual, M, N, rope.glu_limit, rope.glu_alpha, rope.glu_shift, rope.glu_bias);
   }
   return 0;
 }
@@ -835,11 +843,13 @@ static int gemm_tc_run(const void* a, int lda, const void* w, const void* w2, vo
   return 0;
 }
 
-// out = g sigmoid(alpha g) (v + shift) with g = min(a w^T, limit), v = clamp(a w2^T, -limit, limit): the gated epilogue in its clamped form
+// out = g sigmoid(alpha g) (v + shift) with g = min(a w^T + bias, limit), v = clamp(a w2^T + bias, -limit, limit): the gated epilogue
+// in its general form (limit 0: no clamps; `bias` [2 N] float32 = the gate's | the other branch's, or null)
 extern "C" int edgelm_gemm_tc_glu(const void* a, int lda, const void* w, const void* w2, void* out, int ldo, int M, int N, int K,
-                                  int out_dtype, float limit, float alpha, float shift, int* err, cudaStream_t stream) {
-  EL_REFUSE(limit > 0.f && w2 != nullptr, "gemm_tc_glu: needs a positive limit and the second weight");
+                                  int out_dtype, float limit, float alpha, float shift, const float* bias, int* err, cudaStream_t stream) {
+  EL_REFUSE(limit >= 0.f && w2 != nullptr, "gemm_tc_glu: needs a limit (0: none) and the second weight");
   RopeAppend form{};
+  form.glu_bias = bias;
   form.glu_limit = limit;
   form.glu_alpha = alpha;
   form.glu_shift = shift;

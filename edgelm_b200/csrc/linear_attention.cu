@@ -4,7 +4,7 @@
 //   o_t = S_t^T q_t                            (the read-out sees the token's own write)
 //
 // q, k, v are read from the float32 result of the stacked projection (row pitch ldu, column offsets q_off, k_off, v_off,
-// head by head), after `silu_columns` has put them through their activation in place.  Tokens of all sequences are packed along the first
+// head by head), after `silu_columns` has put them through their activation in place (or, with `act`, through silu as they are read).  Tokens of all sequences are packed along the first
 // axis; `seq_tok0[s] .. seq_tok0[s + 1] - 1` are the packed rows of the step's sequence s, `seq_slot[s]` the row of its
 // state [slot][H][E][K].  Everything is float32 in both precisions.
 //
@@ -56,11 +56,13 @@ __device__ __forceinline__ float la_warp_sums(float (&acc)[U], int lane) {
 
 constexpr int LA_WARPS = 8;
 
+__device__ __forceinline__ float scan_silu(float z) { return z / (1.0f + expf(-z)); }
+
 template <int NK, int U>
 __global__ void __launch_bounds__(LA_WARPS * 32)
 decay_scan_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                   float* __restrict__ state, float* __restrict__ o, const int32_t* __restrict__ seq_tok0,
-                  const int32_t* __restrict__ seq_slot, int H, int K, int E) {
+                  const int32_t* __restrict__ seq_slot, int H, int K, int E, int act) {
   pdl_launch_dependents();
   pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -96,11 +98,14 @@ decay_scan_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, in
     for (int x = 0; x < U; ++x) {
       acc[x] = 0.f;
       if (tb + x < t1) {
-        const float vj = in.vj[x];
+        // (`act`: silu here instead of a pass of its own; every warp of a head repeats it for the keys and queries, which
+        // costs less than a launch when a sequence brings one token)
+        const float vj = act ? scan_silu(in.vj[x]) : in.vj[x];
 #pragma unroll
         for (int k = 0; k < NK; ++k) {
-          S[k] = fmaf(a, S[k], in.kk[x][k] * vj);
-          acc[x] = fmaf(S[k], in.qq[x][k], acc[x]);
+          const float kv = act ? scan_silu(in.kk[x][k]) : in.kk[x][k], qv = act ? scan_silu(in.qq[x][k]) : in.qq[x][k];
+          S[k] = fmaf(a, S[k], kv * vj);
+          acc[x] = fmaf(S[k], qv, acc[x]);
         }
       }
     }
@@ -347,14 +352,14 @@ extern "C" int edgelm_silu_columns(float* u, int ldu, int off, int n, int n_toke
 
 extern "C" int edgelm_decay_scan(const float* u, int ldu, int q_off, int k_off, int v_off, const float* decay, float* state, float* o,
                                  const int32_t* seq_tok0, const int32_t* seq_slot, int n_seqs, int H, int K, int E, int n_tokens,
-                                 cudaStream_t stream) {
+                                 int act, cudaStream_t stream) {
   if (n_seqs == 0 || n_tokens == 0) return 0;
   EL_REFUSE(n_seqs > 0 && H > 0 && E > 0 && ldu > 0 && q_off >= 0 && k_off >= 0 && v_off >= 0, "decay_scan: bad sizes");
   EL_REFUSE(K >= 1 && K <= 256, "decay_scan: a key size of %d is not taken (1 to 256)", K);
   // a warp a value channel, whatever the block: with few (sequence, head) pairs, blocks of two warps spread the channels over more SMs
   const int warps = (long long)n_seqs * H * ((E + LA_WARPS - 1) / LA_WARPS) >= 2 * 148 ? LA_WARPS : 2;
   const dim3 grid(n_seqs * H, (E + warps - 1) / warps), block(warps * 32);
-#define EL_SCAN(NK, U) launch_pdl(pdl_bit_for_tokens(n_tokens), decay_scan_kernel<NK, U>, dim3(grid), dim3(block), (size_t)(0), stream, u, ldu, q_off, k_off, v_off, decay, state, o, seq_tok0, seq_slot, H, K, E)
+#define EL_SCAN(NK, U) launch_pdl(pdl_bit_for_tokens(n_tokens), decay_scan_kernel<NK, U>, dim3(grid), dim3(block), (size_t)(0), stream, u, ldu, q_off, k_off, v_off, decay, state, o, seq_tok0, seq_slot, H, K, E, act)
   if (K <= 32) EL_SCAN(1, 8);
   else if (K <= 64) EL_SCAN(2, 8);
   else if (K <= 128) EL_SCAN(4, 4);

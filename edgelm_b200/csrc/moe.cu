@@ -131,7 +131,10 @@ moe_route_scored_kernel(const TH* __restrict__ h, const float* __restrict__ wr, 
       float bc = -INFINITY;
       for (int e = 0; e < E; ++e)
         if (c[e] > bc) { bc = c[e]; best = e; }
-      if (best < 0) {       // (nothing left to choose from: fewer allowed experts than `top`, or NaN scores)
+      if (best < 0)         // fewer allowed experts than `top`: the left-out ones follow in the order of their numbers
+        for (int e = 0; e < E && best < 0; ++e)
+          if (c[e] == -INFINITY) best = e;
+      if (best < 0) {       // (nothing left at all: NaN scores)
         idx[(size_t)t * top + k] = -1;
         wts[(size_t)t * top + k] = 0.f;
         continue;
@@ -139,7 +142,7 @@ moe_route_scored_kernel(const TH* __restrict__ h, const float* __restrict__ wr, 
       idx[(size_t)t * top + k] = best;
       wts[(size_t)t * top + k] = z[best];
       picked += z[best];
-      c[best] = -INFINITY;
+      c[best] = NAN;        // taken (compares false with everything; a left-out expert stays at minus infinity)
     }
     const float norm = scale / (picked + 1e-20f);
     for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= norm;

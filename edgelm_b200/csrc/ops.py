@@ -225,9 +225,10 @@ def _splitk_ready():
         lib().edgelm_gemm_tc_splitk(_p(_splitk_scratch), SPLITK_SCRATCH_BYTES, 1)
 
 
-def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None, glu=None):
+def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None, glu=None, glu_bias=None):
     """out = a @ w.T (+ epilogue) on the tcgen05 tensor cores: bfloat16 operands, float32 accumulation.  `glu` (limit, alpha,
-    shift) with the gated epilogue: out = g sigmoid(alpha g) (v + shift), g = min(a @ w.T, limit), v = clamp(a @ w2.T, -limit, limit)."""
+    shift) with the gated epilogue: out = g sigmoid(alpha g) (v + shift), g = min(a @ w.T, limit), v = clamp(a @ w2.T, -limit, limit)
+    (limit 0: no clamps); `glu_bias` [2 N] float32: the two branches' biases, added before the unit."""
     _splitk_ready()
     _need(a.dim() == 2 and w.dim() == 2 and out.dim() == 2, "gemm_tc: 2-D operands")
     M, K = a.shape
@@ -238,10 +239,12 @@ def gemm_tc(a, w, out, err, epilogue=EPI_STORE, w2=None, residual=None, glu=None
     _need(w2 is None or (w2.dtype == w.dtype and w2.shape == w.shape and w2.is_contiguous()), "gemm_tc: second weight")
     if residual is not None:
         _need(residual.dtype == torch.float32 and residual.shape == out.shape and residual.stride() == out.stride(), "gemm_tc: residual layout")
-    if glu is not None:
-        _need(epilogue == EPI_SWIGLU and w2 is not None and residual is None and glu[0] > 0, "gemm_tc: the clamped gated epilogue needs both weights and a limit")
+    if glu is not None or glu_bias is not None:
+        glu = glu if glu is not None else GLU_SWIGLU
+        _need(epilogue == EPI_SWIGLU and w2 is not None and residual is None and glu[0] >= 0, "gemm_tc: the general gated epilogue needs both weights")
+        _need(glu_bias is None or (glu_bias.dtype == torch.float32 and glu_bias.is_cuda and glu_bias.is_contiguous() and glu_bias.numel() == 2 * N), "gemm_tc: the gated unit's biases")
         _check(lib().edgelm_gemm_tc_glu(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), M, N, K, _dt(out), ctypes.c_float(glu[0]),
-                                        ctypes.c_float(glu[1]), ctypes.c_float(glu[2]), _p(err), _stream()), launches=0)
+                                        ctypes.c_float(glu[1]), ctypes.c_float(glu[2]), _p(glu_bias), _p(err), _stream()), launches=0)
     else:
         _check(lib().edgelm_gemm_tc(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), _p(residual), M, N, K, _dt(out),
                                     epilogue, _p(err), _stream()), launches=0)
@@ -1036,10 +1039,11 @@ def silu_columns(u, off, n):
     _check(lib().edgelm_silu_columns(_p(u), u.stride(0), int(off), int(n), u.shape[0], _stream()))
 
 
-def decay_scan(u, q_off, k_off, v_off, decay, state, o, seq_tok0, seq_slot, n_seqs, heads, k_dim, v_dim):
+def decay_scan(u, q_off, k_off, v_off, decay, state, o, seq_tok0, seq_slot, n_seqs, heads, k_dim, v_dim, act=None):
     """Per head S <- decay_h S + k_t v_t^T, then o_t = S^T q_t, over the step's tokens in order.  q, k (heads x k_dim) and v
     (heads x v_dim) are columns of u [T, *] float32 from q_off, k_off, v_off; decay [heads] float32; state [slots, heads,
-    v_dim, k_dim] float32; o [T, heads v_dim] float32."""
+    v_dim, k_dim] float32; o [T, heads v_dim] float32.  `act` "silu": q, k and v pass it as they are read (every warp of a head
+    again: for steps of few tokens, where that is cheaper than `silu_columns` ahead)."""
     _f32(decay, "decay"); _f32(state, "state"); _f32(o, "o")
     _i32(seq_tok0, "seq_tok0"); _i32(seq_slot, "seq_slot")
     T = u.shape[0]
@@ -1047,7 +1051,7 @@ def decay_scan(u, q_off, k_off, v_off, decay, state, o, seq_tok0, seq_slot, n_se
     _need(max(q_off, k_off) + heads * k_dim <= u.shape[1] and v_off + heads * v_dim <= u.shape[1] and o.shape == (T, heads * v_dim), "decay_scan: shapes")
     _need(decay.numel() == heads and tuple(state.shape[1:]) == (heads, v_dim, k_dim), "decay_scan: decay or state")
     _check(lib().edgelm_decay_scan(_p(u), u.stride(0), int(q_off), int(k_off), int(v_off), _p(decay), _p(state), _p(o), _p(seq_tok0), _p(seq_slot),
-                                   int(n_seqs), int(heads), int(k_dim), int(v_dim), T, _stream()))
+                                   int(n_seqs), int(heads), int(k_dim), int(v_dim), T, 1 if act == "silu" else 0, _stream()))
 
 
 DECAY_CHUNK = 64        # tokens of a chunk of the chunked form (LC in linear_attention.cu)

@@ -100,12 +100,13 @@ class DecayLinearAttention(Part):
                                   tiles.tok0, tiles.ntok, tiles.count, self.heads, self.d, self.e,
                                   act="silu" if self.act == "silu" else None, scratch=scratch)
         else:
-            if self.act == "silu":
+            in_scan = ctx.all_single         # one token a sequence: the activation inside the walk saves its launch
+            if self.act == "silu" and not in_scan:
                 with ctx.prof("linear_attn_act"):
                     ops.silu_columns(u, 0, self.g_off)
             with ctx.prof("linear_attn_scan"):
                 ops.decay_scan(u, 0, self.k_off, self.v_off, self.decay, cache.state, o, ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs,
-                               self.heads, self.d, self.e)
+                               self.heads, self.d, self.e, act="silu" if self.act == "silu" and in_scan else None)
         on = ws.alloc((T, self.inner), self.dtype)
         with ctx.prof("linear_attn_gate_norm"):
             ops.gated_group_norm(o, u[:, self.g_off:], self.norm_w, on, 1, self.eps, gate_first=False, gate_act="sigmoid")

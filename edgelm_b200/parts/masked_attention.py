@@ -61,8 +61,13 @@ def most_keys(mask, size):
 
 # Steps of one token a sequence: with at least so many query heads to a key head the tiled kernel is used (a tile = one
 # token, its rows = the heads that share the key head, so a key row is staged once for all of them), its pages dealt to
-# several blocks; with fewer, a block per (token, head) whose warps share the keys.
+# several blocks; with fewer, a block per (token, head) whose warps share the keys, unless a token may see more than
+# SPLIT_KEYS_FROM keys (no mask, or a long one) and the step has too few (token, head) pairs to fill the device with such
+# blocks: then the walk over one pair's keys is what the step waits for (8 sequences of 9 heads over 2,048 keys: 72 blocks, 184
+# us a layer; 72 with the tiled kernel's splits sharing the walk), however few rows a tile has.  With a block a pair for every
+# SM and more the tiled kernel loses: it stages every key for a tile of one row (8 sequences of 32 heads: 183 -> 254 us).
 SHARED_KEYS_MIN_GROUP = 8
+SPLIT_KEYS_FROM = 1024
 MAX_SPLITS = 32
 _ones = {}
 
@@ -237,7 +242,8 @@ class MaskedAttention(Part):
                               eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
         a = ws.alloc((T, self.nh * self.maps * self.dv), torch.float32 if self.diff else self.dtype)
         with ctx.prof("attn_masked"):
-            if ctx.all_single and self.nh // self.nkv >= SHARED_KEYS_MIN_GROUP:
+            if ctx.all_single and (self.nh // self.nkv >= SHARED_KEYS_MIN_GROUP or
+                                   (most_keys(self.mask, self.mask_size) > SPLIT_KEYS_FROM and T * self.nh * self.maps < 2 * ctx.n_sms)):
                 splits = decode_splits(ctx, self.nkv * self.maps, self.nh // self.nkv, self.mask, self.mask_size)
                 part = ws.alloc((T * self.nh * self.maps * splits * (2 + self.dv),), torch.float32) if splits > 1 else None
                 tseq, ttok0, tntok, tpos0 = single_token_tiles(ctx)

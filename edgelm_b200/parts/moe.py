@@ -12,7 +12,8 @@ Options, each with its constants in the spec:
               v = clamp(W_up h, -limit, limit) (absent: silu(g) v)
     router    {"kind": "scored", ...}: scores s = softmax(z) over ALL experts; the choice takes the `top` largest of s + a
               correction per expert (a tensor, `names["correction"]`), looking only inside the `keep` of `groups` equal groups
-              of neighbouring experts whose largest corrected score is largest (other experts count as minus infinity);
+              of neighbouring experts whose largest corrected score is largest (other experts count as minus infinity: if the
+              kept groups hold fewer than `top` experts, the others follow in the order of their numbers);
               the weights are the chosen experts' s over their sum (+ 1e-20), times `scale`.  `identity`: so many router
               outputs after the experts' belong to identity experts, which have no tensors and return their input (they
               are scored, corrected, grouped and chosen like the others).  This router has no bias.
@@ -49,8 +50,6 @@ class MixtureOfExperts(Part):
             raise ConfigError(f"moe: {self.top} of {self.n_experts} experts and {self.identity} identity experts (up to 1024)")
         if self.router == "scored" and (self.groups < 1 or self.routed % self.groups or not 1 <= self.keep <= self.groups):
             raise ConfigError(f"moe: {self.routed} routed experts in {self.groups} groups of which {self.keep} are kept")
-        if self.router == "scored" and self.keep * (self.routed // self.groups) < self.top:
-            raise ConfigError(f"moe: {self.keep} groups of {self.routed // self.groups} experts cannot give {self.top} choices")
         self.shared = env.build("ffn", spec["shared"]) if spec.get("shared") is not None else None
         self.w_gate = self.w_up = self.w_down = self.w_router = self.b_router = self.correction = None
 

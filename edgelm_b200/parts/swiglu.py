@@ -2,8 +2,9 @@
 (adarsh-sgh/edgelm src/kernels_ref.cpp:143-160, tools/elm.py:140-152).  Gate and up never reach
 memory: the activation is the epilogue of their matrix product, the residual sum that of the
 down projection.  With `bias` (a suffix of the tensors' names) all three projections have biases: x += Wd (silu(Wg h + bg) *
-(Wu h + bu)) + bd.  Gate and up then run as one product over the two weights stacked, whose float32 sums feed the gated unit's
-kernel together with the biases; the down projection's bias is added to the residual stream after its product."""
+(Wu h + bu)) + bd.  Prompt steps in bfloat16 add the two biases in the same tensor-core epilogue; other steps run gate and up as one
+product over the two weights stacked, whose float32 sums feed the gated unit's kernel together with the biases.  The down
+projection's bias is added to the residual stream after its product."""
 import torch
 
 from ..csrc import ops
@@ -61,8 +62,14 @@ class SwiGLU(Part):
         """x += feed_forward(h); with `accumulate` False, x = feed_forward(h) (float32), for an arrangement that
         norms the sublayer's output before the residual sum."""
         mid = ctx.ws.alloc((h.shape[0], self.inter), self.dtype)
-        if self.bias:
-            gu = ctx.ws.alloc((h.shape[0], 2 * self.inter), torch.float32)
+        T, F = h.shape[0], self.inter
+        w_gate, w_up = (self.w_gu[:F], self.w_gu[F:]) if self.bias else (None, None)
+        if self.bias and T > linear.FEW_ROWS and self.dtype == torch.bfloat16 and ops.gemm_tc_takes(linear.as_tensor(h), w_gate, mid, w_up):
+            # prompt steps in bfloat16: the two products share a tile, biases and activation are the product's epilogue
+            with ctx.prof("gate_up_swiglu"):
+                ops.gemm_tc(linear.as_tensor(h), w_gate, mid, ctx.err, epilogue=linear.EPI_SWIGLU, w2=w_up, glu_bias=self.b_gu)
+        elif self.bias:
+            gu = ctx.ws.alloc((T, 2 * F), torch.float32)
             with ctx.prof("gate_up"):
                 linear.matmul(ctx, h, self.w_gu, gu, prefetch=(self.w_down,))
             with ctx.prof("swiglu_bias"):

@@ -70,7 +70,6 @@ def test_refusals():
                          (lambda c: c["layers"][0]["mixer"]["left"]["rot"].update(dims=18), "rotated dimensions"),
                          (lambda c: c["layers"][1]["mlp"]["router"].update(top=10), "of 6 experts"),
                          (lambda c: c["layers"][1]["mlp"]["router"]["groups"].update(count=4), "groups"),
-                         (lambda c: (c["layers"][1]["mlp"]["router"]["groups"].update(keep=1), c["layers"][1]["mlp"]["router"].update(top=4)), "cannot give 4 choices"),
                          (lambda c: c["layers"][1]["mlp"]["expert"].update(limit=0.0), "limit"),
                          (lambda c: c.update(logit_softcap=-1.0), "logit_softcap"),
                          (lambda c: c["loop"].update(stop=5), "loop"),

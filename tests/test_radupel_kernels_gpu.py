@@ -41,10 +41,12 @@ def test_decayed_linear_attention_over_steps(H, d, e, decay):
         seqslot = i32([slots[s] for s, _, _ in live])
         u = f32(np.concatenate([raw[s][a:a + n] for s, a, n in live]))
         keep = u[:, C:].clone()
-        ops.silu_columns(u, 0, C)
+        inside = all(n == 1 for _, _, n in live)          # (steps of one token a sequence: the activation inside the walk)
+        if not inside:
+            ops.silu_columns(u, 0, C)
         assert torch.equal(u[:, C:], keep)
         o = torch.full((u.shape[0], H * e), float("nan"), device=DEV)
-        ops.decay_scan(u, 0, H * d, 2 * H * d, f32(decay), state, o, tok0, seqslot, len(live), H, d, e)
+        ops.decay_scan(u, 0, H * d, 2 * H * d, f32(decay), state, o, tok0, seqslot, len(live), H, d, e, act="silu" if inside else None)
         o = o.cpu().numpy()
         at = 0
         for s, a, n in live:
@@ -166,6 +168,24 @@ def test_gated_unit_with_biases(out_dtype):
     assert (np.abs(mid.float().cpu().numpy() - want) <= rel * (1.0 + np.abs(want))).all()
 
 
+@pytest.mark.parametrize("M,N,K", [(200, 40, 64), (17, 320, 320), (2048, 1536, 576), (130, 72, 1032)])
+def test_biases_in_the_tensor_core_gated_epilogue(M, N, K):
+    """silu(a Wg^T + bg) (a Wu^T + bu) as the epilogue of the tcgen05 product of both weights, for one tile, many tiles and the
+    sizes that split K."""
+    g = np.random.default_rng(M + N)
+    bf = lambda x: torch.tensor(x, dtype=torch.bfloat16, device=DEV)
+    a, wg, wu = bf(g.normal(size=(M, K))), bf(g.normal(size=(N, K)) / np.sqrt(K)), bf(g.normal(size=(N, K)) / np.sqrt(K))
+    bias = f32(g.uniform(-1, 1, 2 * N))
+    mid = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert ops.gemm_tc_takes(a, wg, mid, wu)
+    ops.gemm_tc(a, wg, mid, err, epilogue=ops.EPI_SWIGLU, w2=wu, glu_bias=bias)
+    ad, b = a.double().cpu().numpy(), bias.double().cpu().numpy()
+    want = plain.silu(ad @ wg.double().cpu().numpy().T + b[:N]) * (ad @ wu.double().cpu().numpy().T + b[N:])
+    assert (np.abs(mid.float().cpu().numpy() - want) <= 1e-2 * (1.0 + np.abs(want))).all()
+    assert int(err.item()) == 0
+
+
 # ----------------------------------------------------------------------------- softmax attention with a gate per head
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,dk,dv,rot", [(4, 2, 16, 24, 8), (8, 1, 8, 8, 8), (3, 3, 10, 14, 0), (16, 2, 8, 12, 6), (2, 1, 96, 40, 24)])
@@ -235,7 +255,7 @@ def test_gated_softmax_attention(H, G, dk, dv, rot, dtype):
 
 # ----------------------------------------------------------------------------- the scoring router and its experts
 @pytest.mark.parametrize("E,ident,top,groups,keep,negative", [(6, 3, 3, 3, 2, False), (3, 0, 1, 1, 1, False), (5, 1, 2, 2, 1, True), (7, 2, 2, 3, 1, True),
-                                                              (8, 0, 4, 4, 2, False), (2, 2, 2, 1, 1, True), (12, 4, 3, 8, 2, False)])
+                                                              (8, 0, 4, 4, 2, False), (2, 2, 2, 1, 1, True), (12, 4, 3, 8, 2, False), (4, 2, 3, 3, 1, True)])
 def test_scoring_router(E, ident, top, groups, keep, negative):
     """Scores over all routed experts (identity experts too), the choice by corrected scores inside the best groups only (a
     group left out counts as minus infinity, which shows when every corrected score is negative), the weights from the
@@ -256,6 +276,8 @@ def test_scoring_router(E, ident, top, groups, keep, negative):
     c = np.sort(s + corr, axis=1)
     clear = np.diff(c, axis=1).min(axis=1) > 1e-5
     assert clear.mean() > 0.9
+    if keep * (R // groups) < top:       # more choices than the kept groups hold: the rest are the left-out experts in the order of their numbers
+        assert (chosen[:, keep * (R // groups):] < R).all() and (np.diff(chosen[:, keep * (R // groups):], axis=1) > 0).all()
     assert np.array_equal(idx.cpu().numpy()[clear], chosen[clear])
     assert np.abs(wts.cpu().numpy()[clear] - weights[clear]).max() < 1e-5
     assert np.abs(extra.cpu().numpy()[:, 0] - plain.sigmoid(h @ wr[R])).max() < 1e-6
