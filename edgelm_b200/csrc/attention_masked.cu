@@ -274,7 +274,8 @@ __global__ void __launch_bounds__(MA_MAX_WARPS * 32)
 masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vbase, int ldv,
                    const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table,
                    int table_stride, int n_pages, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
-                   const float* __restrict__ sink, int vec_k, int maps, const float* __restrict__ gate, int ldg) {
+                   const float* __restrict__ sink, int vec_k, int maps, const float* __restrict__ gate, int ldg, int n_splits,
+                   float* __restrict__ part) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float ma_smem[];
@@ -300,7 +301,11 @@ masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* _
   float o[DVR];
 #pragma unroll
   for (int r = 0; r < DVR; ++r) o[r] = 0.f;
-  for (int c = warp; c < n_chunks; c += NW) {
+  // `n_splits` > 1: the token's chunks of 32 keys are dealt to so many blocks (blockIdx.z), each of which leaves its maximum,
+  // denominator and weighted values for the fold kernel (the sink and the gate join there)
+  const int per_split = (n_chunks + n_splits - 1) / n_splits;
+  const int c_end = min(n_chunks, ((int)blockIdx.z + 1) * per_split);
+  for (int c = blockIdx.z * per_split + warp; c < c_end; c += NW) {
     const int n_here = min(32, n_keys - c * 32);
     float sc = -INFINITY;
     int vrow = -1;
@@ -340,6 +345,20 @@ masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* _
     if (d < dv) wo[warp * dv + d] = o[r];
   }
   __syncthreads();
+  if (n_splits > 1) {
+    float M = -INFINITY, L = 0.f;
+    for (int w2 = 0; w2 < NW; ++w2) M = fmaxf(M, wm[w2]);
+    for (int w2 = 0; w2 < NW; ++w2) L += wm[w2] == -INFINITY ? 0.f : wl[w2] * expf(wm[w2] - M);
+    float* dst = part + (((size_t)t * HV + h) * n_splits + blockIdx.z) * (2 + dv);
+    if (threadIdx.x == 0) { dst[0] = M; dst[1] = L; }
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+      float acc = 0.f;
+      for (int w2 = 0; w2 < NW; ++w2)
+        if (wm[w2] != -INFINITY) acc = fmaf(wo[w2 * dv + d], expf(wm[w2] - M), acc);
+      dst[2 + d] = acc;
+    }
+    return;
+  }
   float M = sink ? sink[h / maps] : -INFINITY;
   for (int w2 = 0; w2 < NW; ++w2) M = fmaxf(M, wm[w2]);
   float L = sink ? expf(sink[h / maps] - M) : 0.f;
@@ -727,30 +746,37 @@ static int masked_common_check(const char* what, int H, int G, int dk, int dv, i
 template <typename T, typename TO, int DVR>
 static void launch_masked(const float* q, void* out, const void* kcache, const void* vcache, const int32_t* tok_pos, const int32_t* tok_seq,
                           const int32_t* page_table, int table_stride, int n_pages, int n_tokens, int H, int G, int dk, int dv, float scale,
-                          int mask, int mask_size, const float* sink, int warps, int maps, const float* gate, int ldg, cudaStream_t stream) {
+                          int mask, int mask_size, const float* sink, int warps, int maps, const float* gate, int ldg, int n_splits, float* part,
+                          cudaStream_t stream) {
   const T* vb = vcache ? (const T*)vcache : (const T*)kcache;
   const int ldv = vcache ? dv : dk;
   const int vec_k = (dk % (16 / (int)sizeof(T)) == 0) && ((uintptr_t)kcache % 16 == 0);
   const size_t smem = ((size_t)((dk + 3) & ~3) + (size_t)warps * (2 + dv)) * sizeof(float);
   auto kern = masked_attn_kernel<T, TO, DVR>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  launch_pdl(pdl_bit_for_tokens(n_tokens), kern, dim3(n_tokens, H * maps), dim3(warps * 32), smem, stream, q, (TO*)out, (const T*)kcache, vb, ldv,
-             tok_pos, tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, mask, mask_size, sink, vec_k, maps, gate, ldg);
+  launch_pdl(pdl_bit_for_tokens(n_tokens), kern, dim3(n_tokens, H * maps, n_splits), dim3(warps * 32), smem, stream, q, (TO*)out, (const T*)kcache, vb, ldv,
+             tok_pos, tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, mask, mask_size, sink, vec_k, maps, gate, ldg, n_splits, part);
+  if (n_splits > 1 && cudaPeekAtLastError() == cudaSuccess)
+    launch_pdl(pdl_bit_for_tokens(n_tokens), masked_attn_fold_kernel<TO>, dim3(n_tokens, H * maps), dim3(dv >= 256 ? 256 : 128), (size_t)0, stream,
+               (const float*)part, (TO*)out, sink, H * maps, dv, n_splits, gate, ldg, maps);
 }
 
 // `vcache` null: the values are the first dv dimensions of the key rows.  `max_keys`: the most keys a token of the step sees
-// (chooses how many warps share a token's keys).  `maps` > 1: every query head and key row holds `maps` runs of dk dimensions,
+// (chooses how many warps share a token's keys).  `n_splits` > 1: a token's keys are dealt to so many blocks, whose partial
+// results go through `part` (n_tokens H maps n_splits (2 + dv) floats) and are merged by a second launch.  `maps` > 1: every query head and key row holds `maps` runs of dk dimensions,
 // each an attention of its own over the head's values; q [tokens][H][maps][dk], out [tokens][H][maps][dv].
 extern "C" int edgelm_masked_attn(const float* q, void* out, int out_dtype, const void* kcache, const void* vcache, int dtype,
                                   const int32_t* tok_pos, const int32_t* tok_seq, const int32_t* page_table, int table_stride, int n_pages,
                                   int n_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size, const float* sink,
-                                  int max_keys, int maps, const float* gate, int ldg, cudaStream_t stream) {
+                                  int max_keys, int maps, const float* gate, int ldg, int n_splits, float* part, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
+  EL_REFUSE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || part != nullptr), "masked_attn: %d splits", n_splits);
+  if (n_splits > 1) max_keys = (max_keys + n_splits - 1) / n_splits;
   if (masked_common_check("masked_attn", H, G, dk, dv, mask, mask_size, dtype, out_dtype)) return -1;
   EL_REFUSE(maps >= 1 && H * maps <= 65535 && (maps == 1 || (sink == nullptr && vcache != nullptr)), "masked_attn: %d maps take no sink and values of their own", maps);
   EL_REFUSE(vcache != nullptr || dv <= dk, "masked_attn: values of %d inside keys of %d", dv, dk);
   const int warps = max_keys <= 64 ? 2 : (max_keys <= 256 ? 4 : MA_MAX_WARPS);
-#define EL_MA2(T, TO, DVR) launch_masked<T, TO, DVR>(q, out, kcache, vcache, tok_pos, tok_seq, page_table, table_stride, n_pages, n_tokens, H, G, dk, dv, scale, mask, mask_size, sink, warps, maps, gate, ldg, stream)
+#define EL_MA2(T, TO, DVR) launch_masked<T, TO, DVR>(q, out, kcache, vcache, tok_pos, tok_seq, page_table, table_stride, n_pages, n_tokens, H, G, dk, dv, scale, mask, mask_size, sink, warps, maps, gate, ldg, n_splits, part, stream)
 #define EL_MA(DVR) do { if (dtype == DT_F32) EL_MA2(float, float, DVR); else if (out_dtype == DT_F32) EL_MA2(__nv_bfloat16, float, DVR); else EL_MA2(__nv_bfloat16, __nv_bfloat16, DVR); } while (0)
   if (dv <= 32) EL_MA(1); else if (dv <= 64) EL_MA(2); else if (dv <= 128) EL_MA(4); else if (dv <= 256) EL_MA(8); else EL_MA(16);
 #undef EL_MA

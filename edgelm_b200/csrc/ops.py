@@ -743,17 +743,22 @@ def _head_gate_check(gate, T, nh, what):
     _need(gate is None or (gate.dtype == torch.float32 and gate.is_cuda and gate.shape == (T, nh) and gate.stride(1) == 1), f"{what}: the heads' gate")
 
 
-def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, dk, dv, scale, mask, mask_size, sink, max_keys, maps=1, gate=None):
+def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, dk, dv, scale, mask, mask_size, sink, max_keys, maps=1, gate=None,
+                n_splits=1, part=None):
     """Attention of every token of the step over the keys lo .. its position (`mask`: MASK_CAUSAL lo = 0; MASK_WINDOW the
     last `mask_size` keys; MASK_CHUNK the keys of its own chunk of `mask_size` positions).  q [T, nh dk] float32; out
     [T, nh dv] float32 or the cache's type; `vcache` None: a value is the first dv dimensions of its key row.  `sink`
     (float32 [nh] or None): one more term exp(sink_h) in the denominator.  `max_keys`: the most keys a token sees.
     `maps` > 1: every query head and key row holds `maps` runs of dk dimensions, each an attention of its own over the
     head's values: q [T, nh maps dk], key rows of maps dk, out [T, nh maps dv] (no sink then).  `gate` (float32 [T, nh], rows of
-    any pitch): head h's output is multiplied by sigmoid(gate[t, h]) before it is rounded."""
+    any pitch): head h's output is multiplied by sigmoid(gate[t, h]) before it is rounded.  `n_splits` > 1: a token's keys are
+    dealt to so many blocks, whose partial results go through `part` (float32, T nh maps n_splits (2 + dv) values) and are
+    merged by a second launch: for steps of few tokens over long sequences."""
     _f32(q, "q")
     T = q.shape[0]
     _head_gate_check(gate, T, nh, "masked_attn")
+    _need(n_splits == 1 or (part is not None and part.dtype == torch.float32 and part.is_contiguous() and part.numel() >= T * nh * maps * n_splits * (2 + dv)),
+          "masked_attn: room for the splits' partial results")
     _need(q.shape == (T, nh * maps * dk) and out.is_contiguous() and out.shape == (T, nh * maps * dv), "masked_attn: shapes")
     _need(maps == 1 or (sink is None and vcache is not None), "masked_attn: several maps take no sink and values of their own")
     _masked_cache_check(kcache, vcache, nkv, dk * maps, dv, "masked_attn")
@@ -762,7 +767,8 @@ def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, d
         _i32(t, n)
     _check(lib().edgelm_masked_attn(_p(q), _p(out), _dt(out), _p(kcache), _p(vcache), _dt(kcache), _p(tok_pos), _p(tok_seq), _p(page_table),
                                     page_table.stride(0), kcache.shape[0], T, nh, nkv, dk, dv, ctypes.c_float(scale), int(mask), int(mask_size or 0),
-                                    _p(sink), int(max_keys), int(maps), _p(gate), gate.stride(0) if gate is not None else 0, _stream()))
+                                    _p(sink), int(max_keys), int(maps), _p(gate), gate.stride(0) if gate is not None else 0, int(n_splits), _p(part), _stream()),
+           launches=2 if n_splits > 1 else 1)
 
 
 def masked_attn_tiled(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, nh, nkv,

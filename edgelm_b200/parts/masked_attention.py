@@ -61,13 +61,22 @@ def most_keys(mask, size):
 
 # Steps of one token a sequence: with at least so many query heads to a key head the tiled kernel is used (a tile = one
 # token, its rows = the heads that share the key head, so a key row is staged once for all of them), its pages dealt to
-# several blocks; with fewer, a block per (token, head) whose warps share the keys, unless a token may see more than
-# SPLIT_KEYS_FROM keys (no mask, or a long one) and the step has too few (token, head) pairs to fill the device with such
-# blocks: then the walk over one pair's keys is what the step waits for (8 sequences of 9 heads over 2,048 keys: 72 blocks, 184
-# us a layer; 72 with the tiled kernel's splits sharing the walk), however few rows a tile has.  With a block a pair for every
-# SM and more the tiled kernel loses: it stages every key for a tile of one row (8 sequences of 32 heads: 183 -> 254 us).
+# several blocks; with fewer, a block per (token, head) whose warps share the keys.  Where a token may see more than
+# SPLIT_KEYS_FROM keys (no mask, or a long one) and the step has too few (token, head) pairs for two blocks an SM, the walk over
+# one pair's keys is what the step waits for (8 sequences of 9 heads over 2,048 keys: 72 blocks, 184 us a layer): then a pair's
+# keys are dealt to several such blocks and a second launch merges them.  (The tiled kernel with its splits was tried for
+# these: 72 us a layer with 9 heads of 3 to a key head, but 254 against 183 with 32 heads of one: it stages every key for a
+# tile of one row.)
 SHARED_KEYS_MIN_GROUP = 8
 SPLIT_KEYS_FROM = 1024
+MAX_HEAD_SPLITS = 16
+
+
+def head_splits(ctx, n_pairs, mask, mask_size):
+    """Blocks that share a (token, head) pair's keys in the block-per-pair kernel: about two blocks an SM."""
+    if most_keys(mask, mask_size) <= SPLIT_KEYS_FROM:
+        return 1
+    return min(MAX_HEAD_SPLITS, max(1, (2 * ctx.n_sms + n_pairs - 1) // max(1, n_pairs)))
 MAX_SPLITS = 32
 _ones = {}
 
@@ -242,16 +251,18 @@ class MaskedAttention(Part):
                               eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
         a = ws.alloc((T, self.nh * self.maps * self.dv), torch.float32 if self.diff else self.dtype)
         with ctx.prof("attn_masked"):
-            if ctx.all_single and (self.nh // self.nkv >= SHARED_KEYS_MIN_GROUP or
-                                   (most_keys(self.mask, self.mask_size) > SPLIT_KEYS_FROM and T * self.nh * self.maps < 2 * ctx.n_sms)):
+            if ctx.all_single and self.nh // self.nkv >= SHARED_KEYS_MIN_GROUP:
                 splits = decode_splits(ctx, self.nkv * self.maps, self.nh // self.nkv, self.mask, self.mask_size)
                 part = ws.alloc((T * self.nh * self.maps * splits * (2 + self.dv),), torch.float32) if splits > 1 else None
                 tseq, ttok0, tntok, tpos0 = single_token_tiles(ctx)
                 ops.masked_attn_tiled(q, a, cache.k, cache.v, table, tseq, ttok0, tntok, tpos0, T, 1, self.nh, self.nkv, self.dk, self.dv,
                                       self.scale, self.mask, self.mask_size, self.sink, n_splits=splits, part=part, maps=self.maps, gate=gate)
             elif ctx.all_single:
+                splits = head_splits(ctx, T * self.nh * self.maps, self.mask, self.mask_size)
+                part = ws.alloc((T * self.nh * self.maps * splits * (2 + self.dv),), torch.float32) if splits > 1 else None
                 ops.masked_attn(q, a, cache.k, cache.v, ctx.tok_pos, ctx.tok_seq, table, self.nh, self.nkv, self.dk, self.dv, self.scale,
-                                self.mask, self.mask_size, self.sink, most_keys(self.mask, self.mask_size), maps=self.maps, gate=gate)
+                                self.mask, self.mask_size, self.sink, most_keys(self.mask, self.mask_size), maps=self.maps, gate=gate,
+                                n_splits=splits, part=part)
             else:
                 tiles = ctx.tiles(self.tile_tokens)
                 ops.masked_attn_tiled(q, a, cache.k, cache.v, table, tiles.seq, tiles.tok0, tiles.ntok, tiles.pos0, tiles.count,

@@ -244,6 +244,12 @@ def test_gated_softmax_attention(H, G, dk, dv, rot, dtype):
         out = torch.full((n, H * dv), float("nan"), dtype=dtype, device=DEV)
         ops.masked_attn(q1, out, kv.k, kv.v, i32([p for _, p in live]), i32(list(range(n))), sub, H, G, dk, dv, scale, ops.MASK_CAUSAL, 0, None, 1 << 30, gate=g1)
         assert np.abs(out.float().cpu().numpy() - ref).max() < tol * max(1.0, np.abs(ref).max()), ("single", back)
+        for splits in (2, 5):       # the same kernel with a pair's keys dealt to several blocks (some of which get none)
+            out3 = torch.full((n, H * dv), float("nan"), dtype=dtype, device=DEV)
+            part = torch.full((n * H * splits * (2 + dv),), float("nan"), device=DEV)
+            ops.masked_attn(q1, out3, kv.k, kv.v, i32([p for _, p in live]), i32(list(range(n))), sub, H, G, dk, dv, scale, ops.MASK_CAUSAL, 0, None, 1 << 30,
+                            gate=g1, n_splits=splits, part=part)
+            assert np.abs(out3.float().cpu().numpy() - ref).max() < tol * max(1.0, np.abs(ref).max()), ("single, keys split", back, splits)
         for splits in (1, 3):
             out2 = torch.full((n, H * dv), float("nan"), dtype=dtype, device=DEV)
             part = torch.full((n * H * splits * (2 + dv),), float("nan"), device=DEV)

@@ -203,6 +203,12 @@ def test_attention_with_a_key_range(H, G, dk, dv, kind, size, with_sink, dtype):
         got = out.float().cpu().numpy()
         ref = np.stack([want[s][p].reshape(H * dv) for s, p in live])
         assert np.abs(got - ref).max() < tol * max(1.0, np.abs(ref).max()), ("single", back)
+        for splits in (2, 4):       # the same kernel with a token's keys dealt to several blocks; the sink joins in the merge
+            out1 = torch.full((len(live), H * dv), float("nan"), dtype=dtype, device=DEV)
+            part = torch.full((len(live) * H * splits * (2 + dv),), float("nan"), device=DEV)
+            ops.masked_attn(q, out1, kv.k, kv.v, i32([p for _, p in live]), i32(list(range(len(live)))), table[[s for s, _ in live]].contiguous(), H, G, dk, dv,
+                            scale, mk, ms, sk, 1 << 30 if kind == "causal" else size, n_splits=splits, part=part)
+            assert np.abs(out1.float().cpu().numpy() - ref).max() < tol * max(1.0, np.abs(ref).max()), ("single, keys split", back, splits)
         # the same tokens as tiles of one token, their pages dealt to 1, 3 and 5 blocks whose results a second launch merges
         for splits in (1, 3, 5):
             out2 = torch.full((len(live), H * dv), float("nan"), dtype=dtype, device=DEV)
