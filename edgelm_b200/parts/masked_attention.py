@@ -64,19 +64,22 @@ def most_keys(mask, size):
 # several blocks; with fewer, a block per (token, head) whose warps share the keys.  Where a token may see more than
 # SPLIT_KEYS_FROM keys (no mask, or a long one) and the step has too few (token, head) pairs for two blocks an SM, the walk over
 # one pair's keys is what the step waits for (8 sequences of 9 heads over 2,048 keys: 72 blocks, 184 us a layer): then a pair's
-# keys are dealt to several such blocks and a second launch merges them.  (The tiled kernel with its splits was tried for
-# these: 72 us a layer with 9 heads of 3 to a key head, but 254 against 183 with 32 heads of one: it stages every key for a
-# tile of one row.)
+# keys are dealt to several such blocks and a second launch merges them (8 sequences of 32 heads of one to a key head: 254 ->
+# 143 us a layer), or, from SHARED_KEYS_LONG_GROUP heads to a key head on, the tiled kernel with its splits takes the step (9
+# heads of 3 to a key head: 72 us a layer against 85 with the pairs' keys dealt out; with one head to a key head it stages
+# every key for a tile of one row and loses, 254 against 183 us).
 SHARED_KEYS_MIN_GROUP = 8
 SPLIT_KEYS_FROM = 1024
 MAX_HEAD_SPLITS = 16
+BLOCKS_AN_SM = 2        # (4 and 8 blocks of four warps an SM measured the same within noise)
+SHARED_KEYS_LONG_GROUP = 3
 
 
 def head_splits(ctx, n_pairs, mask, mask_size):
-    """Blocks that share a (token, head) pair's keys in the block-per-pair kernel: about two blocks an SM."""
+    """Blocks that share a (token, head) pair's keys in the block-per-pair kernel: about BLOCKS_AN_SM blocks of four warps an SM."""
     if most_keys(mask, mask_size) <= SPLIT_KEYS_FROM:
         return 1
-    return min(MAX_HEAD_SPLITS, max(1, (2 * ctx.n_sms + n_pairs - 1) // max(1, n_pairs)))
+    return min(MAX_HEAD_SPLITS, max(1, (BLOCKS_AN_SM * ctx.n_sms + n_pairs - 1) // max(1, n_pairs)))
 MAX_SPLITS = 32
 _ones = {}
 
@@ -101,8 +104,9 @@ def decode_splits(ctx, n_kv_heads, group, mask, mask_size):
 
 def splits_room(n_seqs, n_heads, dv):
     """Bytes of the splits' partial results for a step of `n_seqs` single tokens (sequences x splits stays under 2 SMs' worth
-    of blocks plus the sequences themselves; 600 covers devices of up to 300 SMs)."""
-    return nbytes(((600 + n_seqs) * n_heads * (2 + dv),), torch.float32)
+    of blocks plus the sequences themselves, (token, head) pairs x their splits under BLOCKS_AN_SM SMs' worth plus the pairs; 600 and
+    300 cover devices of up to 300 SMs)."""
+    return nbytes((((600 + n_seqs) * n_heads + BLOCKS_AN_SM * 300) * (2 + dv),), torch.float32)
 
 
 @register_mixer("masked_attention")
@@ -251,7 +255,9 @@ class MaskedAttention(Part):
                               eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
         a = ws.alloc((T, self.nh * self.maps * self.dv), torch.float32 if self.diff else self.dtype)
         with ctx.prof("attn_masked"):
-            if ctx.all_single and self.nh // self.nkv >= SHARED_KEYS_MIN_GROUP:
+            pairs = T * self.nh * self.maps
+            long_and_few = ctx.all_single and most_keys(self.mask, self.mask_size) > SPLIT_KEYS_FROM and pairs < 2 * ctx.n_sms
+            if ctx.all_single and (self.nh // self.nkv >= SHARED_KEYS_MIN_GROUP or (long_and_few and self.nh // self.nkv >= SHARED_KEYS_LONG_GROUP)):
                 splits = decode_splits(ctx, self.nkv * self.maps, self.nh // self.nkv, self.mask, self.mask_size)
                 part = ws.alloc((T * self.nh * self.maps * splits * (2 + self.dv),), torch.float32) if splits > 1 else None
                 tseq, ttok0, tntok, tpos0 = single_token_tiles(ctx)
