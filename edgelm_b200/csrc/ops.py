@@ -1016,14 +1016,19 @@ def rglru_gates(u, w_ra, w_ri, gates, blocks):
         head_matmul(u, bw, w_ri, gates[:, W:], bw)
 
 
-def clamped_glu(gu, mid, limit, alpha, shift=1.0, bias=None):
+def clamped_glu(gu, mid, limit, alpha, shift=1.0, bias=None, x=None, x_bias=None):
     """mid = g sigmoid(alpha g) (v + shift) with g = min(gate, limit), v = clamp(up, -limit, limit) (limit 0: no clamps);
-    gu [T, 2 F] float32 = gate | up, `bias` [2 F] float32 added to it first.  limit 0, alpha 1, shift 0: silu(gate) * up."""
+    gu [T, 2 F] float32 = gate | up, `bias` [2 F] float32 added to it first.  limit 0, alpha 1, shift 0: silu(gate) * up.
+    With `x` [T, D] float32 and `x_bias` [D]: x += x_bias in the same launch (the bias of the projection that follows, whose
+    epilogue adds to x)."""
     _f32(gu, "gu")
     T, F = mid.shape
     _need(gu.shape == (T, 2 * F) and mid.is_contiguous(), "clamped_glu: shapes")
     _need(bias is None or (bias.dtype == torch.float32 and bias.is_cuda and bias.is_contiguous() and bias.numel() == 2 * F), "clamped_glu: bias")
-    _check(lib().edgelm_clamped_glu(_p(gu), _p(mid), _dt(mid), T, F, ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift), _p(bias), _stream()))
+    _need((x is None) == (x_bias is None) and (x is None or (x.dtype == torch.float32 and x.is_contiguous() and x.shape[0] == T and x_bias.dtype == torch.float32 and
+                                                             x_bias.is_contiguous() and x_bias.numel() == x.shape[1])), "clamped_glu: the rows that take a bias")
+    _check(lib().edgelm_clamped_glu(_p(gu), _p(mid), _dt(mid), T, F, ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift), _p(bias),
+                                    _p(x), _p(x_bias), x.shape[1] if x is not None else 0, _stream()))
 
 
 def diff_combine(a, out, lam, eps, post, w=None):

@@ -269,9 +269,11 @@ rglru_gates_mma_kernel(const float* __restrict__ u, int ldu, const __nv_bfloat16
 // mid = g sigmoid(alpha g) (v + 1) with g = min(gate, limit), v = clamp(up, -limit, limit); gu [tokens][2 F] float32 = gate | up
 template <typename TO>
 __global__ void clamped_glu_kernel(const float* __restrict__ gu, TO* __restrict__ mid, int F, float limit, float alpha, float shift,
-                                   const float* __restrict__ bias) {
+                                   const float* __restrict__ bias, float* __restrict__ x, const float* __restrict__ x_bias, int D) {
   pdl_launch_dependents();
   pdl_wait();
+  if (x != nullptr)      // the bias of the projection that follows, added to the rows that its residual epilogue adds to
+    for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)blockIdx.x * D + i] += x_bias[i];
   const float* row = gu + (size_t)blockIdx.x * 2 * F;
   for (int i = threadIdx.x; i < F; i += blockDim.x) {
     float g = row[i] + (bias ? bias[i] : 0.f), v = row[F + i] + (bias ? bias[F + i] : 0.f);
@@ -331,14 +333,15 @@ extern "C" int edgelm_rglru_gates(const float* u, int ldu, const void* w_ra, con
 
 // mid = g sigmoid(alpha g) (v + shift) with g = gate + bias, v = up + bias, both clamped (g from above, v on both sides) when
 // limit > 0; `bias` [2 F] may be null.  limit 0, alpha 1, shift 0: SwiGLU.
+// `x` [tokens][D] with `x_bias` [D] (or null): x[t] += x_bias as well, in the same launch.
 extern "C" int edgelm_clamped_glu(const float* gu, void* mid, int out_dtype, int n_tokens, int F, float limit, float alpha, float shift,
-                                  const float* bias, cudaStream_t stream) {
+                                  const float* bias, float* x, const float* x_bias, int D, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && F > 0 && limit >= 0.f, "clamped_glu: bad sizes");
   const dim3 grid(n_tokens), block(F >= 1024 ? 256 : 128);
   const int bit = pdl_bit_for_tokens(n_tokens);
-  if (out_dtype == DT_F32) launch_pdl(bit, clamped_glu_kernel<float>, grid, block, (size_t)0, stream, gu, (float*)mid, F, limit, alpha, shift, bias);
-  else if (out_dtype == DT_BF16) launch_pdl(bit, clamped_glu_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, gu, (__nv_bfloat16*)mid, F, limit, alpha, shift, bias);
+  if (out_dtype == DT_F32) launch_pdl(bit, clamped_glu_kernel<float>, grid, block, (size_t)0, stream, gu, (float*)mid, F, limit, alpha, shift, bias, x, x_bias, D);
+  else if (out_dtype == DT_BF16) launch_pdl(bit, clamped_glu_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, gu, (__nv_bfloat16*)mid, F, limit, alpha, shift, bias, x, x_bias, D);
   else EL_REFUSE(false, "clamped_glu: unknown dtype code %d", out_dtype);
   EL_LAUNCH_CHECK("clamped_glu");
   return 0;

@@ -43,6 +43,7 @@ class DecayLinearAttention(Part):
             raise ConfigError(f"decay_linear_attention: {len(self.decay_values)} decays for {self.heads} heads (one in [0, 1] each)")
         if self.act not in ("silu", "none"):
             raise ConfigError(f"decay_linear_attention: activation '{self.act}' is not known (silu, none)")
+        self.out_scale = 1.0
         self.qk, self.inner = self.heads * self.d, self.heads * self.e
         self.k_off, self.v_off, self.g_off = self.qk, 2 * self.qk, 2 * self.qk + self.inner
         self.d_in = 2 * self.qk + 2 * self.inner            # q | k | v | gate
@@ -62,12 +63,20 @@ class DecayLinearAttention(Part):
         n = self.names
         self.w_in = torch.cat([as_matrix(tensors[prefix + n[k]], self.dtype, device) for k in ("q", "k", "v", "g")], dim=0).contiguous()
         self.norm_w = as_vector(tensors[prefix + n["norm"]], device)
+        if self.out_scale != 1.0:
+            self.norm_w = (self.norm_w * self.out_scale).contiguous()
         self.w_o = as_matrix(tensors[prefix + n["o"]], self.dtype, device)
         self.decay = torch.tensor(self.decay_values, dtype=torch.float64).to(device=device, dtype=torch.float32).contiguous()
         self.powers = ops.decay_powers(self.decay_values).to(device)
 
     def first_weights(self):
         return (self.w_in,)
+
+    def fold_out_scale(self, scale, ask=False):
+        """Multiply this mixer's output by `scale` from now on (before its weights are loaded): the norm's weight takes it."""
+        if not ask:
+            self.out_scale = float(scale)
+        return True
 
     def _chunked(self):
         return ops.decay_chunked_takes(self.d, self.e)

@@ -146,6 +146,15 @@ class MaskedAttention(Part):
         self.tile_tokens = max(1, 32 // (self.nh // self.nkv))
         self.freq = self.b_qkv = self.b_o = self.sink = self.conv_w = self.q_norm = self.k_norm = self.no_tail = None
         self.lam = 0.0
+        self.out_scale = 1.0
+
+    def fold_out_scale(self, scale, ask=False):
+        """Multiply this mixer's output by `scale` from now on (before its weights are loaded), if that costs nothing: the output
+        is linear in the values, and with a convolution on them the values' taps take the constant.  False: it cannot."""
+        can = self.taps > 0 and not self.diff and not self.out_bias
+        if can and not ask:
+            self.out_scale = float(scale)
+        return can
 
     def tile_sizes(self):
         return (self.tile_tokens,)
@@ -202,6 +211,8 @@ class MaskedAttention(Part):
         if self.taps:
             self.conv_w = torch.cat([as_matrix(tensors[prefix + n[k] + n["conv"]], torch.float32, device) for k in ("q", "k", "v")], dim=0).contiguous()
             self.no_tail = torch.zeros((1, 0, self.d_qkv), dtype=torch.float32, device=device)      # (one tap: no earlier row is kept)
+            if self.out_scale != 1.0:
+                self.conv_w[(self.nh + self.nkv) * self.kw:] *= self.out_scale
         if self.qk_norm:
             self.q_norm, self.k_norm = as_vector(tensors[prefix + n["q_norm"]], device), as_vector(tensors[prefix + n["k_norm"]], device)
         if self.diff:

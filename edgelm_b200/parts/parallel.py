@@ -15,6 +15,13 @@ class ParallelMixers(Part):
         self.left_scale, self.right_scale = float(spec["left_scale"]), float(spec["right_scale"])
         self.dtype = env.dtype
         self.parts = (self.left, self.right)
+        # a mixer that can multiply its own output by a constant at no cost (in a weight it applies anyway) is asked to: when
+        # both can, each adds into x through its last product's epilogue and the scaled sum needs no kernel
+        self.folded = all(hasattr(p, "fold_out_scale") for p in self.parts) and \
+            self.left.fold_out_scale(self.left_scale, ask=True) and self.right.fold_out_scale(self.right_scale, ask=True)
+        if self.folded:
+            self.left.fold_out_scale(self.left_scale)
+            self.right.fold_out_scale(self.right_scale)
 
     @property
     def graph_safe(self):
@@ -58,6 +65,15 @@ class ParallelMixers(Part):
         from . import linear
         h = linear.as_tensor(h)
         T, ws = h.shape[0], ctx.ws
+        if self.folded and accumulate:
+            after = ctx.weights_after
+            ctx.weights_after = self.right.first_weights()
+            with ws.frame():
+                self.left.forward(ctx, h, x, cache.get("left"))
+            ctx.weights_after = after
+            with ws.frame():
+                self.right.forward(ctx, h, x, cache.get("right"))
+            return
         y1 = ws.alloc((T, self.hidden), torch.float32)
         y2 = ws.alloc((T, self.hidden), torch.float32)
         after = ctx.weights_after

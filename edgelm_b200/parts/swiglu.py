@@ -63,6 +63,7 @@ class SwiGLU(Part):
         norms the sublayer's output before the residual sum."""
         mid = ctx.ws.alloc((h.shape[0], self.inter), self.dtype)
         T, F = h.shape[0], self.inter
+        down_bias_done = False
         w_gate, w_up = (self.w_gu[:F], self.w_gu[F:]) if self.bias else (None, None)
         if self.bias and T > linear.FEW_ROWS and self.dtype == torch.bfloat16 and ops.gemm_tc_takes(linear.as_tensor(h), w_gate, mid, w_up):
             # prompt steps in bfloat16: the two products share a tile, biases and activation are the product's epilogue
@@ -72,13 +73,14 @@ class SwiGLU(Part):
             gu = ctx.ws.alloc((T, 2 * F), torch.float32)
             with ctx.prof("gate_up"):
                 linear.matmul(ctx, h, self.w_gu, gu, prefetch=(self.w_down,))
-            with ctx.prof("swiglu_bias"):
-                ops.clamped_glu(gu, mid, 0.0, 1.0, shift=0.0, bias=self.b_gu)
+            with ctx.prof("swiglu_bias"):      # (with the residual sum to follow, the down projection's bias joins x here)
+                ops.clamped_glu(gu, mid, 0.0, 1.0, shift=0.0, bias=self.b_gu, x=x if accumulate else None, x_bias=self.b_down if accumulate else None)
+            down_bias_done = accumulate
         else:
             with ctx.prof("gate_up_swiglu"):
                 linear.matmul(ctx, h, self.w_gate, mid, epilogue=linear.EPI_SWIGLU, w2=self.w_up, prefetch=(self.w_down,))
         with ctx.prof("down_proj_residual"):
             linear.matmul(ctx, mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL if accumulate else linear.EPI_STORE,
                           residual=x if accumulate else None, prefetch=ctx.weights_after)
-            if self.b_down is not None:
+            if self.b_down is not None and not down_bias_done:
                 ops.add_row_bias(x, self.b_down)
