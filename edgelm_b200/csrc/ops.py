@@ -803,6 +803,33 @@ def masked_attn_tiled(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, t
            launches=2 if n_splits > 1 else 1)
 
 
+SPLIT_PREFILL_TILE = 64  # new tokens per tile of the split-precision tensor-core prefill kernel (SP_ROWS in attention_mma_split.cu)
+
+
+def attn_prefill_split_takes(dtype, dk, dv):
+    """Whether the tensor-core prompt attention with float32 scores and weights takes this cache type and these head sizes."""
+    return dtype == torch.bfloat16 and dk == dv and dk in (32, 64, 96, 128)
+
+
+def attn_prefill_split(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, nh, nkv, hd, scale, gate=None,
+                       max_keys=0):
+    """Causal attention of a prompt step over the paged bfloat16 cache on the tensor cores with float32 scores and softmax
+    weights: the float32 operand of each product (queries; weights) goes as three bfloat16 terms.  q [T, nh hd] float32; out
+    [T, nh hd] bfloat16; tiles of at most SPLIT_PREFILL_TILE tokens; `page_table` rows are the step's sequences; `gate` as in
+    `masked_attn`."""
+    _f32(q, "q")
+    T = q.shape[0]
+    _need(q.shape == (T, nh * hd) and out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == (T, nh * hd), "attn_prefill_split: shapes")
+    _masked_cache_check(kcache, vcache, nkv, hd, hd, "attn_prefill_split")
+    _need(vcache is not None and kcache.dtype == torch.bfloat16, "attn_prefill_split: a bfloat16 cache with values of their own")
+    _head_gate_check(gate, T, nh, "attn_prefill_split")
+    for t, n in ((page_table, "page_table"), (tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"), (tile_ntok, "tile_ntok"), (tile_pos0, "tile_pos0")):
+        _i32(t, n)
+    _check(lib().edgelm_attn_prefill_split(_p(q), q.stride(0), _p(out), out.stride(0), _p(kcache), _p(vcache), _p(page_table), page_table.stride(0),
+                                           _p(tile_seq), _p(tile_tok0), _p(tile_ntok), _p(tile_pos0), int(n_tiles), nh, nkv, hd, ctypes.c_float(scale),
+                                           _p(gate), gate.stride(0) if gate is not None else 0, int(max_keys), _stream()))
+
+
 # ----------------------------------------------------------------------------- gated delta rule
 def delta_prepare(qkv, u, b_off, a_off, a_log, dt_bias, bg, heads, kv_heads, d, e, unit_eps, q_scale):
     """qkv [T, G d | G d | H e] float32, in place: every query and key head becomes x / sqrt(sum(x^2) + unit_eps), queries

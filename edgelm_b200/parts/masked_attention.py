@@ -156,8 +156,14 @@ class MaskedAttention(Part):
             self.out_scale = float(scale)
         return can
 
+    def _on_tensor_cores(self):
+        """Whether prompt steps take the tensor-core kernel with float32 scores and weights (three bfloat16 terms for each
+        float32 operand): a causal mask, no sink, one map a head, a bfloat16 cache, key = value head sizes that it takes."""
+        return (self.mask == ops.MASK_CAUSAL and self.maps == 1 and "sink" not in self.names and
+                ops.attn_prefill_split_takes(self.dtype, self.dk, self.dv))
+
     def tile_sizes(self):
-        return (self.tile_tokens,)
+        return (self.tile_tokens, ops.SPLIT_PREFILL_TILE) if self._on_tensor_cores() else (self.tile_tokens,)
 
     def sizes(self):
         out = {"heads": self.nh, "kv_heads": self.nkv, "head_dim": self.dk, "v_head_dim": self.dv, "rot_dims": self.rot,
@@ -280,6 +286,10 @@ class MaskedAttention(Part):
                 ops.masked_attn(q, a, cache.k, cache.v, ctx.tok_pos, ctx.tok_seq, table, self.nh, self.nkv, self.dk, self.dv, self.scale,
                                 self.mask, self.mask_size, self.sink, most_keys(self.mask, self.mask_size), maps=self.maps, gate=gate,
                                 n_splits=splits, part=part)
+            elif self._on_tensor_cores():
+                tiles = ctx.tiles(ops.SPLIT_PREFILL_TILE)
+                ops.attn_prefill_split(q, a, cache.k, cache.v, table, tiles.seq, tiles.tok0, tiles.ntok, tiles.pos0, tiles.count, self.nh, self.nkv,
+                                       self.dk, self.scale, gate=gate, max_keys=max(p + n for p, n in zip(ctx.seq_first_positions, ctx.seq_lengths)))
             else:
                 tiles = ctx.tiles(self.tile_tokens)
                 ops.masked_attn_tiled(q, a, cache.k, cache.v, table, tiles.seq, tiles.tok0, tiles.ntok, tiles.pos0, tiles.count,

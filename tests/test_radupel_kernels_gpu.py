@@ -188,7 +188,8 @@ def test_biases_in_the_tensor_core_gated_epilogue(M, N, K):
 
 # ----------------------------------------------------------------------------- softmax attention with a gate per head
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,dk,dv,rot", [(4, 2, 16, 24, 8), (8, 1, 8, 8, 8), (3, 3, 10, 14, 0), (16, 2, 8, 12, 6), (2, 1, 96, 40, 24)])
+@pytest.mark.parametrize("H,G,dk,dv,rot", [(4, 2, 16, 24, 8), (8, 1, 8, 8, 8), (3, 3, 10, 14, 0), (16, 2, 8, 12, 6), (2, 1, 96, 40, 24), (4, 2, 64, 64, 32),
+                                           (2, 1, 96, 96, 24), (3, 3, 32, 32, 0), (2, 2, 128, 128, 64)])
 def test_gated_softmax_attention(H, G, dk, dv, rot, dtype):
     """Rotation and append from rows that hold q | k | v | gate, then causal attention with each head's output times the
     sigmoid of its gate: prompt steps in tiles, steps of one token (a block per head, and pages dealt to several blocks).
@@ -232,6 +233,21 @@ def test_gated_softmax_attention(H, G, dk, dv, rot, dtype):
     ops.masked_attn_tiled(qo, out, kv.k, kv.v, table, tseq, ttok0, tntok, tpos0, count, tile, H, G, dk, dv, scale, ops.MASK_CAUSAL, 0, None, gate=u[:, d_qkv:])
     ref = np.concatenate(want)
     assert np.abs(out.float().cpu().numpy() - ref).max() < tol * max(1.0, np.abs(ref).max())
+    if ops.attn_prefill_split_takes(dtype, dk, dv):
+        # the tensor-core kernel with float32 scores and weights, whole sequences and then their second halves over the first
+        tseq, ttok0, tntok, tpos0, count = make_tiles(lengths, [0] * len(lengths), ops.SPLIT_PREFILL_TILE)
+        out = torch.full((u.shape[0], H * dv), float("nan"), dtype=dtype, device=DEV)
+        ops.attn_prefill_split(qo, out, kv.k, kv.v, table, tseq, ttok0, tntok, tpos0, count, H, G, dk, scale, gate=u[:, d_qkv:], max_keys=max(lengths))
+        got = out.float().cpu().numpy()
+        assert np.abs(got - ref).max() < tol * max(1.0, np.abs(ref).max())
+        halves = [(n // 3, n - n // 3) for n in lengths]
+        starts0 = np.concatenate([[0], np.cumsum(lengths)])
+        sel = torch.tensor(np.concatenate([np.arange(starts0[s] + a, starts0[s] + a + n) for s, (a, n) in enumerate(halves)]), device=DEV)
+        tseq, ttok0, tntok, tpos0, count = make_tiles([n for _, n in halves], [a for a, _ in halves], ops.SPLIT_PREFILL_TILE)
+        out = torch.full((len(sel), H * dv), float("nan"), dtype=dtype, device=DEV)
+        ops.attn_prefill_split(qo[sel].contiguous(), out, kv.k, kv.v, table, tseq, ttok0, tntok, tpos0, count, H, G, dk, scale,
+                               gate=u[sel][:, d_qkv:], max_keys=max(lengths))
+        assert np.abs(out.float().cpu().numpy() - ref[sel.cpu().numpy()]).max() < tol * max(1.0, np.abs(ref).max())
     # steps of one token a sequence at the sequences' ends and around a page border
     starts = np.concatenate([[0], np.cumsum(lengths)])
     for back in (0, 1, 64, 66):
@@ -257,6 +273,29 @@ def test_gated_softmax_attention(H, G, dk, dv, rot, dtype):
                                   dk, dv, scale, ops.MASK_CAUSAL, 0, None, n_splits=splits, part=part, gate=g1)
             assert np.abs(out2.float().cpu().numpy() - ref).max() < tol * max(1.0, np.abs(ref).max()), ("single, split", back, splits)
     assert int(err.item()) == 0
+
+
+def test_tensor_core_attention_keeps_float32_scores_and_weights():
+    """Queries so large that their rounding to bfloat16 would move the scores by a good part of 1, and values of very
+    different sizes under weights of very different sizes: the kernel's output follows the float64 attention of the float32
+    queries, not that of rounded queries nor that of rounded weights."""
+    g = np.random.default_rng(4)
+    H, G, d, n = 2, 1, 64, 200
+    bf = lambda a: torch.tensor(a, dtype=torch.bfloat16).double().numpy()
+    q = torch.tensor(g.normal(size=(n, H, d)) * 10.0, dtype=torch.float32).double().numpy()
+    k, v = bf(g.normal(size=(n, G, d))), bf(g.normal(size=(n, G, d)) * np.exp(g.normal(size=(n, 1, 1)) * 3))
+    scale = 1.0 / np.sqrt(d)
+    want = plain.causal_softmax_attention(q, k, v, scale).reshape(n, H * d)
+    rounded_q = plain.causal_softmax_attention(bf(q), k, v, scale).reshape(n, H * d)
+    kv = PagedKV([n], G, d, d, torch.bfloat16, seed=1)
+    kv.put(0, k, v)
+    tseq, ttok0, tntok, tpos0, count = make_tiles([n], [0], ops.SPLIT_PREFILL_TILE)
+    out = torch.full((n, H * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attn_prefill_split(f32(q.reshape(n, H * d)), out, kv.k, kv.v, i32(kv.table), tseq, ttok0, tntok, tpos0, count, H, G, d, scale, max_keys=n)
+    got = out.float().cpu().numpy()
+    size = np.abs(want).max(axis=1, keepdims=True) + 1e-9
+    ours, theirs = (np.abs(got - want) / size).max(), (np.abs(rounded_q - want) / size).max()
+    assert ours < 6e-3 and theirs > 5 * ours, (ours, theirs)       # (6e-3: the output's own rounding to bfloat16)
 
 
 # ----------------------------------------------------------------------------- the scoring router and its experts
