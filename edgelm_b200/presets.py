@@ -56,17 +56,17 @@ def _redenex(vocab, width, ff, pattern, rec_width, rec_blocks, heads, kv_heads, 
 def _radupel(vocab, width, ff, pattern, loop, heads, kv_heads, lin_heads, experts, expert_ff, shared_ff):
     """A Radupel-shaped model: every layer a softmax attention (heads of 64, half of each rotated, a convolution of 4 taps on
     q, k and v, a gate per head) beside a linear attention with a constant decay per head (heads of 64 x 64), with a dense
-    feed-forward ("d") or a mixture of `experts` clamped experts plus two identity experts in two groups, two chosen of the
-    better group, and a shared expert ("m"), in the order of `pattern`; `loop` (start, stop, times) or None."""
+    feed-forward ("d") or a mixture of `experts` clamped experts plus four identity experts in three groups, two chosen out of
+    the two better groups, and a shared expert ("m"), in the order of `pattern`; `loop` (start, stop, times) or None."""
     decay = [round(1.0 - 2.0 ** -(3.0 + 6.0 * h / max(1, lin_heads - 1)), 6) for h in range(lin_heads)]
     mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "conv": 4, "scale": 0.125,
-                      "rot": {"base": 250000.0, "dims": 32}},
+                      "rot": {"base": 1000000.0, "dims": 32}},
              "left_scale": 1.0, "right": {"heads": lin_heads, "dim": 64, "vdim": 64, "decay": decay}, "right_scale": 1.0}
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
-           "router": {"experts": experts, "top": 2, "identity": 2, "groups": {"count": 2, "keep": 1}, "scale": 2.5},
+           "router": {"experts": experts, "top": 2, "identity": 4, "groups": {"count": 3, "keep": 2}, "scale": 2.0},
            "shared": {"ff": shared_ff, "limit": 7.0}}
-    out = {"architecture": "Radupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "max_positions": 8192,
+    out = {"architecture": "Radupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 50.0, "max_positions": 8192,
            "layers": [{"type": "parallel", "mixer": mixer, "mlp": dense if c == "d" else moe} for c in pattern]}
     if loop:
         out["loop"] = dict(zip(("start", "stop", "times"), loop))

@@ -49,18 +49,18 @@ def moe(ff, limit, experts, top, identity, groups, keep, scale, shared):
 # head: decoding shares staged keys and splits pages) and one key head per query head; value heads wider and narrower than
 # key heads in both mixers; rotation of a part of a head, of all of it, and none; 1 to 4 taps and no convolution; key sizes
 # of the linear attention under, at and over a warp's 32 lanes; one to three chosen of 3 to 9 routed experts with 0 to 3
-# identity experts, one group, two of three, one of two; shared expert or none; layers without a feed-forward; a loop in the
+# identity experts, one group, two of three, one of three; shared expert or none; layers without a feed-forward; a loop in the
 # middle run three times, a loop from the first layer, no loop; a soft cap or none; widths that are no multiple of 8.
 CFG_A = {"architecture": "Radupel", "vocab": 173, "width": 64, "norm": {"eps": 1e-5}, "logit_softcap": 12.0,
          "loop": {"start": 1, "stop": 3, "times": 3}, "layers": [
-    layer(left(4, 2, 16, 24, 2, {"base": 700.0, "dims": 8}, 0.3), right(2, 24, 16, (0.9, 0.999)), 1.3, 0.7, dense(40)),
+    layer(left(4, 2, 16, 24, 2, {"base": 700.0, "dims": 8}, 0.3), right(2, 24, 16, (0.9, 0.998)), 1.3, 0.7, dense(40)),
     layer(left(8, 1, 8, 8, 4, {"base": 10000.0, "dims": 8}, 0.4), right(3, 40, 8, (0.3, 0.97, 1.0)), 0.8, 1.1,
           moe(24, 1.5, 6, 3, 3, 3, 2, 1.7, (32, 1.0))),
     layer(left(2, 2, 24, 8, 3, {"base": 50.0, "dims": 12}, 0.25), right(1, 32, 48, (0.95,)), 1.0, 1.0, None),
     layer(left(3, 1, 12, 20, None, None, 0.35), right(4, 8, 8, (0.5, 0.8, 0.99, 0.9)), 0.6, 1.4, moe(16, 0.8, 3, 1, 0, None, None, 1.0, None)),
 ]}
 CFG_B = {"architecture": "Radupel", "vocab": 97, "width": 50, "norm": {"eps": 3e-4}, "layers": [
-    layer(left(3, 3, 10, 14, 1, None, 0.35), right(2, 20, 30, (0.85, 0.6)), 1.1, 0.9, moe(20, 3.0, 5, 2, 1, 2, 1, 2.5, (18, 2.0))),
+    layer(left(3, 3, 10, 14, 1, None, 0.35), right(2, 20, 30, (0.85, 0.6)), 1.1, 0.9, moe(20, 3.0, 5, 2, 1, 3, 2, 2.2, (18, 2.0))),
     layer(left(2, 1, 32, 20, 3, {"base": 90.0, "dims": 32}, 0.2), right(5, 10, 6, (0.99, 0.9, 0.7, 0.4, 0.995)), 0.9, 1.2, dense(30)),
     layer(left(6, 3, 8, 40, 2, {"base": 3000.0, "dims": 4}, 0.5), right(2, 64, 12, (0.98, 0.93)), 1.2, 0.5, dense(18)),
 ]}

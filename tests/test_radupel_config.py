@@ -41,7 +41,7 @@ def test_the_plan_reads_every_constant():
     assert att["num_heads"] == 4 and att["num_kv_heads"] == 2 and att["head_dim"] == 16
     lin = mix["right"]
     assert lin.kind == "decay_linear_attention" and lin["heads"] == 2 and lin["head_dim"] == 24 and lin["v_head_dim"] == 16
-    assert lin["decay"] == (0.9, 0.999) and lin["eps"] == 1e-5 and lin["activation"] == "silu"
+    assert lin["decay"] == (0.9, 0.998) and lin["eps"] == 1e-5 and lin["activation"] == "silu"
     assert plan.layers[0].ffn.kind == "swiglu" and plan.layers[0].ffn["bias"] == ".b" and plan.layers[0].ffn["intermediate_size"] == 40
     ffn = plan.layers[1].ffn
     assert ffn.kind == "moe" and ffn["experts"] == 6 and ffn["top"] == 3 and ffn["intermediate_size"] == 24 and ffn["glu"] == (1.5, 1.702, 1.0)

@@ -185,13 +185,13 @@ def test_a_far_key_decides(tmp_path):
 
 
 def test_a_state_left_long_ago_decides(tmp_path):
-    """Linear attention with decays of 0.999 and 1 and the softmax attention's share turned down: what the state took in
+    """Linear attention with decays of 0.998 and 1 and the softmax attention's share turned down: what the state took in
     hundreds of tokens ago is most of it.  Decoding, pieces and a slot used again must carry it, and start it from zero,
     exactly."""
     from edgelm_b200.engine.engine import Engine, StepEntry
     cfg = {"architecture": "Radupel", "vocab": 90, "width": 40, "norm": {"eps": 1e-6}, "loop": {"start": 0, "stop": 2, "times": 2}, "layers": [
-        M.layer(M.left(2, 1, 8, 8, 2, None, 0.3), M.right(2, 24, 12, (0.999, 1.0)), 0.1, 1.5, None),
-        M.layer(M.left(1, 1, 8, 8, None, None, 0.3), M.right(3, 8, 40, (1.0, 0.995, 0.999)), 0.1, 1.5, M.dense(24))]}
+        M.layer(M.left(2, 1, 8, 8, 2, None, 0.3), M.right(2, 24, 12, (0.998, 1.0)), 0.1, 1.5, None),
+        M.layer(M.left(1, 1, 8, 8, None, None, 0.3), M.right(3, 8, 40, (1.0, 0.995, 0.998)), 0.1, 1.5, M.dense(24))]}
     d = M.write_dir(str(tmp_path / "slow"), cfg, 9)
     pcfg, PW = plain.load(d)
     eng = Engine.from_dir(d, dtype="float32", max_tokens=1024)

@@ -17,7 +17,7 @@ DEV = "cuda:0"
 
 
 # ----------------------------------------------------------------------------- linear attention with a constant decay
-@pytest.mark.parametrize("H,d,e,decay", [(2, 24, 16, (0.9, 0.999)), (3, 40, 8, (0.3, 0.97, 1.0)), (1, 32, 48, (0.95,)), (4, 8, 8, (0.5, 0.8, 0.99, 0.0)),
+@pytest.mark.parametrize("H,d,e,decay", [(2, 24, 16, (0.9, 0.998)), (3, 40, 8, (0.3, 0.97, 1.0)), (1, 32, 48, (0.95,)), (4, 8, 8, (0.5, 0.8, 0.99, 0.0)),
                                          (2, 64, 12, (0.98, 0.93)), (1, 72, 130, (0.97,)), (2, 130, 5, (0.9, 0.6)), (1, 256, 3, (0.99,))])
 def test_decayed_linear_attention_over_steps(H, d, e, decay):
     """silu of the projections and the recurrence, fed in pieces (down to one token) on state rows in no particular order; a
@@ -57,7 +57,7 @@ def test_decayed_linear_attention_over_steps(H, d, e, decay):
     assert torch.isnan(state[1]).all()
 
 
-@pytest.mark.parametrize("H,d,e,decay", [(2, 24, 16, (0.9, 0.999)), (3, 40, 8, (0.3, 0.97, 1.0)), (1, 32, 48, (0.95,)), (4, 8, 8, (0.5, 0.8, 0.99, 0.0)),
+@pytest.mark.parametrize("H,d,e,decay", [(2, 24, 16, (0.9, 0.998)), (3, 40, 8, (0.3, 0.97, 1.0)), (1, 32, 48, (0.95,)), (4, 8, 8, (0.5, 0.8, 0.99, 0.0)),
                                          (2, 64, 64, (0.98, 0.93)), (1, 72, 128, (0.97,)), (2, 128, 5, (0.9, 0.6)), (1, 1, 1, (0.99,))])
 def test_decayed_linear_attention_chunk_by_chunk(H, d, e, decay):
     """The same recurrence in its chunked form, which prompt steps take: pieces that end inside a chunk, at a chunk's edge and
@@ -343,7 +343,7 @@ def test_clamped_experts_identity_and_shared(T, D, E, ident, top, ff, shared, dt
          "correction": torch.tensor(g.uniform(-0.1, 0.1, R), dtype=torch.float32).double().numpy()}
     for e in range(E):
         W[f"e{e}.gate"], W[f"e{e}.up"], W[f"e{e}.down"] = rnd(g.normal(size=(ff, D)) * 2 / np.sqrt(D)), rnd(g.normal(size=(ff, D)) * 2 / np.sqrt(D)), rnd(g.normal(size=(D, ff)) / np.sqrt(ff))
-    mlp = {"expert": {"ff": ff, "limit": limit}, "router": {"experts": E, "top": top, "identity": ident, "scale": 2.5}}
+    mlp = {"expert": {"ff": ff, "limit": limit}, "router": {"experts": E, "top": top, "identity": ident, "scale": 1.9}}
     if shared:
         W["shared.gate"], W["shared.up"], W["shared.down"] = rnd(g.normal(size=(shared, D)) / np.sqrt(D)), rnd(g.normal(size=(shared, D)) / np.sqrt(D)), rnd(g.normal(size=(D, shared)) / np.sqrt(shared))
         W["shared.sg"] = torch.tensor(g.normal(size=(1, D)) / np.sqrt(D), dtype=torch.float32).double().numpy()
@@ -355,7 +355,7 @@ def test_clamped_experts_identity_and_shared(T, D, E, ident, top, ff, shared, dt
     wts = torch.empty(T, top, device=DEV)
     wr = np.concatenate([W["router"], W["shared.sg"]]) if shared else W["router"]
     gate = torch.empty(T, 1, device=DEV) if shared else None
-    ops.moe_route_scored(hd, f32(wr), f32(W["correction"]), idx, wts, top, R, 1, 1, 2.5, extra=gate)
+    ops.moe_route_scored(hd, f32(wr), f32(W["correction"]), idx, wts, top, R, 1, 1, 1.9, extra=gate)
     z = h @ W["router"].T
     s = np.exp(z - z.max(1, keepdims=True)); s /= s.sum(1, keepdims=True)
     c = np.sort(s + W["correction"], axis=1)
