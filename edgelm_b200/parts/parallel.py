@@ -65,14 +65,15 @@ class ParallelMixers(Part):
         from . import linear
         h = linear.as_tensor(h)
         T, ws = h.shape[0], ctx.ws
-        if self.folded and accumulate:
+        if self.folded:
+            # the mixers scale their own outputs: the left one stores or adds as the caller asks, the right one adds to that
             after = ctx.weights_after
             ctx.weights_after = self.right.first_weights()
             with ws.frame():
-                self.left.forward(ctx, h, x, cache.get("left"))
+                self.left.forward(ctx, h, x, cache.get("left"), accumulate=accumulate)
             ctx.weights_after = after
             with ws.frame():
-                self.right.forward(ctx, h, x, cache.get("right"))
+                self.right.forward(ctx, h, x, cache.get("right"), accumulate=True)
             return
         y1 = ws.alloc((T, self.hidden), torch.float32)
         y2 = ws.alloc((T, self.hidden), torch.float32)
