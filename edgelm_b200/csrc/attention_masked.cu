@@ -57,13 +57,27 @@ constexpr int MA_WARPS = 4;
 // dimensions side by side (the maps of a differential attention): then each run is rotated by itself.  With `q_norm` /
 // `k_norm` (dk / maps weights each, shared by all heads and runs) every run is first divided by its root mean square
 // (eps inside the root) and multiplied by the weight.
+// With `conv_w` ([channels][taps], channels = the q | k | v columns) every channel first passes a causal filter over time,
+// out_t[c] = sum_j w[c][j] in_(t - taps + 1 + j)[c] with in = qkv + bias; inputs from before the step come from `conv_state`
+// [slot][taps - 1][channels] (oldest first; zeros before a sequence's start), so the projection's result goes through the
+// filter, the norm, the rotation and into the cache without a trip to memory between.  `move_tail` (steps of one token a
+// sequence only: the thread of a channel is then the only one that touches the sequence's tail of that channel): the tail
+// moves on by the token's input here; other steps leave that to `conv_tail_update` afterwards.
+struct ConvAhead {
+  const float* w = nullptr;
+  float* state = nullptr;
+  const int32_t* seq_tok0 = nullptr;
+  const int32_t* seq_slot = nullptr;
+  int taps = 0, move_tail = 0;
+};
+
 template <typename T>
 __global__ void __launch_bounds__(MA_WARPS * 32)
 rotate_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, float* __restrict__ q_out,
                      const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table,
                      int table_stride, int n_pages, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int dk, int dv,
                      int rot, int interleaved, const double* __restrict__ freq, int* __restrict__ err, int maps,
-                     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, int ldq) {
+                     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, int ldq, ConvAhead conv) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float ra_stage[];   // MA_WARPS rows of dk floats
@@ -81,10 +95,29 @@ rotate_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bi
   const int in_page = pos % PAGE;
   const float* row = qkv + (size_t)t * ldq;       // (ldq: the rows' pitch; a row may hold more than q | k | v)
   float* sh = ra_stage + warp * dk;
+  // channel c after the filter over time (and the tail moved on, if this thread is to do it)
+  const int C = (H + G) * dk + G * dv;
+  const int cs = conv.w ? tok_seq[t] : 0, ct0 = conv.w ? conv.seq_tok0[cs] : 0, ck = t - ct0;
+  float* tail = conv.w ? conv.state + (size_t)conv.seq_slot[cs] * (conv.taps - 1) * C : nullptr;
+  auto filtered = [&](int c) -> float {
+    const float ib = bias ? bias[c] : 0.f;
+    float acc = 0.f;
+    for (int j = 0; j < conv.taps; ++j) {
+      const int r = ck - (conv.taps - 1) + j;
+      const float v = r >= 0 ? qkv[(size_t)(ct0 + r) * ldq + c] + ib : tail[(size_t)(conv.taps - 1 + r) * C + c];
+      acc = fmaf(conv.w[(size_t)c * conv.taps + j], v, acc);
+    }
+    if (conv.move_tail && conv.taps > 1) {      // (every row of the tail was read above; row j takes row j + 1, the last one the token's input)
+      for (int j = 0; j + 2 < conv.taps; ++j) tail[(size_t)j * C + c] = tail[(size_t)(j + 1) * C + c];
+      tail[(size_t)(conv.taps - 2) * C + c] = row[c] + ib;
+    }
+    return acc;
+  };
   for (int head = blockIdx.y * MA_WARPS + warp; head < H + G; head += gridDim.y * MA_WARPS) {
     const float* src = row + (size_t)head * dk;
     const float* b = bias ? bias + (size_t)head * dk : nullptr;
-    for (int i = lane; i < dk; i += 32) sh[i] = src[i] + (b ? b[i] : 0.f);
+    if (conv.w) for (int i = lane; i < dk; i += 32) sh[i] = filtered(head * dk + i);
+    else for (int i = lane; i < dk; i += 32) sh[i] = src[i] + (b ? b[i] : 0.f);
     __syncwarp();
     const int ds = dk / maps;
     const float* nw = head < H ? q_norm : k_norm;
@@ -110,7 +143,7 @@ rotate_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bi
   const float* vb = bias ? bias + (size_t)(H + G) * dk : nullptr;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < G * dv; i += gridDim.y * blockDim.x) {
     const int g = i / dv, j = i - g * dv;
-    vcache[(((size_t)page * G + g) * PAGE + in_page) * dv + j] = from_f32<T>(vrow[i] + (vb ? vb[i] : 0.f));
+    vcache[(((size_t)page * G + g) * PAGE + in_page) * dv + j] = from_f32<T>(conv.w ? filtered((H + G) * dk + i) : vrow[i] + (vb ? vb[i] : 0.f));
   }
 }
 
@@ -647,8 +680,13 @@ extern "C" int edgelm_diff_combine(const float* a, void* out, int out_dtype, flo
 extern "C" int edgelm_rotate_append(const float* qkv, const float* bias, float* q_out, const int32_t* tok_pos, const int32_t* tok_seq,
                                     const int32_t* page_table, int table_stride, int n_pages, void* kcache, void* vcache, int dtype,
                                     int n_tokens, int H, int G, int dk, int dv, int rot, int interleaved, const double* freq, int* err,
-                                    int maps, const float* q_norm, const float* k_norm, float eps, int ldq, cudaStream_t stream) {
+                                    int maps, const float* q_norm, const float* k_norm, float eps, int ldq, const float* conv_w, int taps,
+                                    float* conv_state, const int32_t* seq_tok0, const int32_t* seq_slot, int move_tail, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
+  EL_REFUSE(conv_w == nullptr || (taps >= 1 && seq_tok0 != nullptr && seq_slot != nullptr && (taps == 1 || conv_state != nullptr)),
+            "rotate_append: a filter of %d taps needs the sequences' first rows, their slots and the tails", taps);
+  ConvAhead conv;
+  conv.w = conv_w; conv.state = conv_state; conv.seq_tok0 = seq_tok0; conv.seq_slot = seq_slot; conv.taps = taps; conv.move_tail = move_tail;
   if (ldq == 0) ldq = (H + G) * dk + G * dv;
   EL_REFUSE(ldq >= (H + G) * dk + G * dv, "rotate_append: rows of %d values do not hold the heads", ldq);
   EL_REFUSE(maps >= 1 && dk % maps == 0 && rot <= dk / maps, "rotate_append: %d maps of a head of %d with %d rotated dimensions", maps, dk, rot);
@@ -660,10 +698,10 @@ extern "C" int edgelm_rotate_append(const float* qkv, const float* bias, float* 
   const int bit = pdl_bit_for_tokens(n_tokens);
   if (dtype == DT_F32)
     launch_pdl(bit, rotate_append_kernel<float>, grid, block, smem, stream, qkv, bias, q_out, tok_pos, tok_seq, page_table, table_stride,
-               n_pages, (float*)kcache, (float*)vcache, H, G, dk, dv, rot, interleaved, freq, err, maps, q_norm, k_norm, eps, ldq);
+               n_pages, (float*)kcache, (float*)vcache, H, G, dk, dv, rot, interleaved, freq, err, maps, q_norm, k_norm, eps, ldq, conv);
   else if (dtype == DT_BF16)
     launch_pdl(bit, rotate_append_kernel<__nv_bfloat16>, grid, block, smem, stream, qkv, bias, q_out, tok_pos, tok_seq, page_table,
-               table_stride, n_pages, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, H, G, dk, dv, rot, interleaved, freq, err, maps, q_norm, k_norm, eps, ldq);
+               table_stride, n_pages, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, H, G, dk, dv, rot, interleaved, freq, err, maps, q_norm, k_norm, eps, ldq, conv);
   else
     EL_REFUSE(false, "rotate_append: unknown dtype code %d", dtype);
   EL_LAUNCH_CHECK("rotate_append");

@@ -663,12 +663,16 @@ def _masked_cache_check(kcache, vcache, nkv, dk, dv, what):
 
 
 def rotate_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache, nh, nkv, dk, dv, rot, interleaved, freq, err,
-                  maps=1, q_norm=None, k_norm=None, eps=0.0):
+                  maps=1, q_norm=None, k_norm=None, eps=0.0, conv_w=None, conv_state=None, seq_tok0=None, seq_slot=None, n_seqs=0):
     """qkv [T, nh dk + nkv dk + nkv dv] float32 (+ bias): the first `rot` dimensions of every query and key head are rotated
     by position * freq (float64 frequencies; pairs (2i, 2i + 1) if `interleaved`, else (i, i + rot/2)); queries go to q_out
     [T, nh dk] float32, keys and values to their places in the cache pages.  `maps` > 1: a head of dk dimensions is `maps`
     runs of dk / maps side by side, each rotated (its first `rot` dimensions) by itself.  `q_norm` / `k_norm` (float32
-    [dk / maps]): every run is first divided by its root mean square (`eps` inside the root) and multiplied by the weight."""
+    [dk / maps]): every run is first divided by its root mean square (`eps` inside the root) and multiplied by the weight.
+    `conv_w` (float32 [columns, taps]): every column of qkv + bias first passes a causal filter over time, as `conv_act` computes
+    it (inputs from before the step out of `conv_state` [slots, taps - 1, columns], which is moved on to the step's last
+    inputs: in the same launch when every sequence brings one token, by a second launch otherwise); `seq_tok0`, `seq_slot`,
+    `n_seqs` as for `conv_act`."""
     _need(qkv.dtype == torch.float32 and qkv.is_cuda and qkv.dim() == 2 and qkv.stride(1) == 1, "rotate_append: qkv must be float32 rows")
     _f32(q_out, "q_out")
     T = qkv.shape[0]
@@ -682,10 +686,23 @@ def rotate_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache
         _need(w is None or (w.dtype == torch.float32 and w.is_cuda and w.is_contiguous() and w.numel() == dk // maps), f"rotate_append: {n}")
     for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (page_table, "page_table")):
         _i32(t, n)
+    taps, single = 0, False
+    if conv_w is not None:
+        _f32(conv_w, "conv_w")
+        taps = conv_w.shape[1]
+        _need(conv_w.shape[0] == qkv.shape[1] and seq_tok0 is not None and seq_slot is not None and n_seqs > 0, "rotate_append: the filter's shapes")
+        _need(taps == 1 or (conv_state is not None and conv_state.dtype == torch.float32 and conv_state.is_contiguous() and
+                            tuple(conv_state.shape[1:]) == (taps - 1, qkv.shape[1])), "rotate_append: the filter's tails")
+        _i32(seq_tok0, "seq_tok0"); _i32(seq_slot, "seq_slot")
+        single = T == int(n_seqs)
     _check(lib().edgelm_rotate_append(_p(qkv), _p(bias), _p(q_out), _p(tok_pos), _p(tok_seq), _p(page_table), page_table.stride(0),
                                       kcache.shape[0], _p(kcache), _p(vcache), _dt(kcache), T, nh, nkv, dk, dv, int(rot),
                                       1 if interleaved else 0, _p(freq), _p(err), int(maps), _p(q_norm), _p(k_norm), ctypes.c_float(eps),
-                                      qkv.stride(0), _stream()))
+                                      qkv.stride(0), _p(conv_w), int(taps), _p(conv_state if taps > 1 else None), _p(seq_tok0), _p(seq_slot),
+                                      1 if single else 0, _stream()))
+    if conv_w is not None and taps > 1 and not single:
+        _check(lib().edgelm_conv_tail_update(_p(qkv), qkv.stride(0), 0, _p(conv_state), _p(seq_tok0), _p(seq_slot), int(n_seqs), qkv.shape[1], int(taps),
+                                             _p(bias), _stream()))
 
 
 def latent_prepare(u, kv_off, has_kv, q_out, q_pitch, q_off, copy_q, norm_w, eps, tok_pos, tok_seq, page_table, kcache, nh, d, rd, r, freq, err,

@@ -536,6 +536,17 @@ extern "C" int edgelm_conv_act(const float* u, int ldu, int off, const float* w,
   return 0;
 }
 
+// The tails after a step, by themselves: for a caller whose own kernel ran the filter (and read the old tails) already.
+extern "C" int edgelm_conv_tail_update(const float* u, int ldu, int off, float* state, const int32_t* seq_tok0, const int32_t* seq_slot,
+                                       int n_seqs, int C, int taps, const float* in_bias, cudaStream_t stream) {
+  if (n_seqs == 0 || taps <= 1) return 0;
+  EL_REFUSE(n_seqs > 0 && C > 0 && ldu >= off + C, "conv_tail_update: bad sizes");
+  const dim3 grid(n_seqs, (C + 255) / 256), block(256);
+  launch_pdl(pdl_bit_for_tokens(n_seqs), conv_state_update_kernel, grid, block, (size_t)0, stream, u, ldu, off, state, seq_tok0, seq_slot, C, taps, in_bias);
+  EL_LAUNCH_CHECK("conv_tail_update");
+  return 0;
+}
+
 extern "C" int edgelm_conv_silu(const float* u, int ldu, int off, const float* w, const float* b, float* state, float* out,
                                 const int32_t* tok_seq, const int32_t* seq_tok0, const int32_t* seq_slot, int n_tokens, int n_seqs,
                                 int C, int taps, int update_state, cudaStream_t stream) {

@@ -242,7 +242,7 @@ class MaskedAttention(Part):
 
     def workspace_bytes(self, n_tokens, n_seqs):
         f32 = torch.float32
-        return (nbytes((n_tokens, self.d_in), f32) + (nbytes((n_tokens, self.d_qkv), f32) if self.taps else 0) + nbytes((n_tokens, self.nh * self.kw), f32) +
+        return (nbytes((n_tokens, self.d_in), f32) + nbytes((n_tokens, self.nh * self.kw), f32) +
                 nbytes((n_tokens, self.nh * self.maps * self.dv), f32 if self.diff else self.dtype) +
                 (nbytes((n_tokens, self.nh * self.dv), self.dtype) if self.diff else 0) + nbytes((n_tokens, self.hidden), self.dtype) +
                 splits_room(n_seqs, self.nh * self.maps, self.dv))
@@ -256,20 +256,18 @@ class MaskedAttention(Part):
         qkv = u[:, :self.d_qkv]
         gate = u[:, self.d_qkv:] if self.head_gate else None
         bias = self.b_qkv
-        if self.taps:
+        conv = None
+        if self.taps:       # (the filter over time runs inside the kernel that norms, rotates and appends)
             conv = cache.get("conv") if self.taps > 1 else None
             cache = cache["kv"] if self.taps > 1 else cache
-            mixed = ws.alloc((T, self.d_qkv), torch.float32)
-            with ctx.prof("qkv_conv"):
-                ops.conv_act(u, 0, self.conv_w, None, conv.state if conv is not None else self.no_tail, mixed, ctx.tok_seq, ctx.seq_tok0,
-                             ctx.seq_slots, ctx.n_seqs, update_state=True, in_bias=bias, act=None)
-            qkv, bias = mixed, None
         q = ws.alloc((T, self.nh * self.kw), torch.float32)
         table = ctx.page_table(cache.group)
         with ctx.prof("rotate_append"):
             ops.rotate_append(qkv, bias, q, ctx.tok_pos, ctx.tok_seq, table, cache.k, cache.v, self.nh, self.nkv, self.kw, self.dv,
                               self.rot, self.interleaved, self.freq, ctx.err, maps=self.maps, q_norm=self.q_norm, k_norm=self.k_norm,
-                              eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
+                              eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0,
+                              conv_w=self.conv_w if self.taps else None, conv_state=conv.state if conv is not None else None,
+                              seq_tok0=ctx.seq_tok0 if self.taps else None, seq_slot=ctx.seq_slots if self.taps else None, n_seqs=ctx.n_seqs)
         a = ws.alloc((T, self.nh * self.maps * self.dv), torch.float32 if self.diff else self.dtype)
         with ctx.prof("attn_masked"):
             pairs = T * self.nh * self.maps

@@ -275,6 +275,51 @@ def test_gated_softmax_attention(H, G, dk, dv, rot, dtype):
     assert int(err.item()) == 0
 
 
+@pytest.mark.parametrize("taps", [1, 2, 4])
+def test_filter_over_time_inside_rotation_and_append(taps):
+    """The short causal filter on q, k and v, the rotation and the cache append in one kernel, fed in pieces (down to one token,
+    shorter than the filter's tail, and steps of one token a sequence, which move the tails on themselves) on tail rows in no
+    particular order: what reaches q and the cache pages is the plain filter of the whole sequence, rotated."""
+    from edgelm_b200.parts.rope import rotary_frequencies
+    g = np.random.default_rng(taps)
+    H, G, dk, dv, rot = 3, 1, 12, 6, 8
+    C = (H + G) * dk + G * dv
+    total, cuts, slots = [43, 6, 1, 70], [[5, 1, 37], [2, 4], [1], [1, 1, 68]], [4, 0, 2, 5]
+    raw = [torch.tensor(g.normal(size=(n, C + 2)), dtype=torch.float32).double().numpy() for n in total]     # (two more columns: rows hold more than q | k | v)
+    w = torch.tensor(g.normal(0, 0.6, size=(C, taps)), dtype=torch.float32).double().numpy()
+    freq = rotary_frequencies(rot, 300.0, None)
+    kv = PagedKV(total, G, dk, dv, torch.float32, seed=2)
+    kv.v.fill_(0)
+    table = i32(kv.table)
+    tails = torch.zeros(7, taps - 1, C, device=DEV)
+    tails[1].fill_(float("nan"))
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got_q = [np.zeros((n, H * dk)) for n in total]
+    for step in steps_of(total, cuts):
+        live = [(s, a, n) for s, (a, n) in enumerate(step) if n]
+        tok0, tok_seq = packed([n for _, _, n in live])
+        u = f32(np.concatenate([raw[s][a:a + n] for s, a, n in live]))
+        pos = i32(np.concatenate([np.arange(a, a + n) for _, a, n in live]))
+        q = torch.full((u.shape[0], H * dk), float("nan"), device=DEV)
+        ops.rotate_append(u[:, :C], None, q, pos, tok_seq, table[[s for s, _, _ in live]].contiguous(), kv.k, kv.v, H, G, dk, dv, rot, False, freq.to(DEV), err,
+                          conv_w=f32(w), conv_state=tails if taps > 1 else None, seq_tok0=tok0, seq_slot=i32([slots[s] for s, _, _ in live]), n_seqs=len(live))
+        q = q.cpu().numpy()
+        at = 0
+        for s, a, n in live:
+            got_q[s][a:a + n] = q[at:at + n]
+            at += n
+    for s, n in enumerate(total):
+        y = plain.causal_conv(raw[s][:, :C], w)
+        qw = plain.rotate_half_pairs(y[:, :H * dk].reshape(n, H, dk), np.arange(n), rot, 300.0)
+        kw = plain.rotate_half_pairs(y[:, H * dk:(H + G) * dk].reshape(n, G, dk), np.arange(n), rot, 300.0)
+        assert np.abs(got_q[s] - qw.reshape(n, H * dk)).max() < 1e-5
+        for p in range(n):
+            page = kv.table[s, p // PAGE]
+            assert np.abs(kv.k[page, :, p % PAGE].cpu().numpy() - kw[p]).max() < 1e-5
+            assert np.abs(kv.v[page, :, p % PAGE].cpu().numpy() - y[p, (H + G) * dk:].reshape(G, dv)).max() < 1e-5
+    assert int(err.item()) == 0 and (taps == 1 or torch.isnan(tails[1]).all())
+
+
 def test_tensor_core_attention_keeps_float32_scores_and_weights():
     """Queries so large that their rounding to bfloat16 would move the scores by a good part of 1, and values of very
     different sizes under weights of very different sizes: the kernel's output follows the float64 attention of the float32
