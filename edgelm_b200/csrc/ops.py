@@ -896,8 +896,10 @@ def moe_route(h, wr, br, idx, wts, top):
 def moe_route_scored(h, wr, correction, idx, wts, top, n_experts, groups=1, keep=1, scale=1.0, extra=None):
     """The router that scores every expert: s = softmax(wr[:n_experts] h) over all experts (float32); the `top` experts with the
     largest s + correction are chosen (first of equal ones), with `groups` > 1 only among the `keep` groups of neighbouring
-    experts whose best corrected score is largest; wts = s of the chosen over their sum (+ 1e-20), times `scale`.  Rows of
-    `wr` after the first `n_experts` give `extra` [T, rows] = sigmoid(row . h).  idx of a choice that could not be made: -1."""
+    experts whose best corrected score is largest (the others count as minus infinity: when the kept groups hold fewer than `top`
+    experts, the left-out ones follow in the order of their numbers); wts = s of the chosen over their sum (+ 1e-20), times
+    `scale`.  Rows of `wr` after the first `n_experts` give `extra` [T, rows] = sigmoid(row . h).  idx of a choice that could not
+    be made (scores that are not numbers): -1."""
     _f32(wr, "router weight"); _f32(wts, "wts"); _i32(idx, "idx")
     T, D = h.shape
     n_extra = wr.shape[0] - n_experts
