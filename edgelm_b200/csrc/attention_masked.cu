@@ -358,17 +358,29 @@ masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* _
     m = m_new;
 #pragma unroll
     for (int r = 0; r < DVR; ++r) o[r] *= corr;
-#pragma unroll 4
-    for (int j = 0; j < n_here; ++j) {
-      const float wj = __shfl_sync(0xffffffffu, w, j);
-      const int vr_i = __shfl_sync(0xffffffffu, vrow, j);
-      if (vr_i < 0) continue;
-      const T* vr = vbase + (size_t)vr_i * ldv;
+    // the values of VB keys are requested before the first is used: with one key's loads at a time a chunk of 32 keys was 32
+    // trips to memory one after the other (8 sequences x 32 heads over 2,048 keys: 105 -> 84 us a layer in a launch list)
+    constexpr int VB = DVR <= 2 ? 16 : (DVR <= 4 ? 8 : 4);
+    for (int j0 = 0; j0 < n_here; j0 += VB) {
+      float wv[VB];
+      T vals[VB][DVR];
 #pragma unroll
-      for (int r = 0; r < DVR; ++r) {
-        const int d = lane + 32 * r;
-        if (d < dv) o[r] = fmaf(wj, to_f32(vr[d]), o[r]);
+      for (int x = 0; x < VB; ++x) {
+        const int j = min(j0 + x, 31);
+        const float wj = __shfl_sync(0xffffffffu, w, j);
+        const int vr_i = __shfl_sync(0xffffffffu, vrow, j);
+        wv[x] = j0 + x < n_here && vr_i >= 0 ? wj : 0.f;
+        const T* vr = vbase + (size_t)max(vr_i, 0) * ldv;
+#pragma unroll
+        for (int r = 0; r < DVR; ++r) {
+          const int d = lane + 32 * r;
+          vals[x][r] = d < dv && wv[x] != 0.f ? vr[d] : from_f32<T>(0.f);
+        }
       }
+#pragma unroll
+      for (int x = 0; x < VB; ++x)
+#pragma unroll
+        for (int r = 0; r < DVR; ++r) o[r] = fmaf(wv[x], to_f32(vals[x][r]), o[r]);
     }
   }
   if (lane == 0) { wm[warp] = m; wl[warp] = l; }

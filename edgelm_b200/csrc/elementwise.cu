@@ -306,7 +306,7 @@ extern "C" int edgelm_rmsnorm_pair(float* x, const float* add, const float* w1, 
                                    int rows, int dim, float eps, cudaStream_t stream) {
   if (rows == 0) return 0;
   EL_REFUSE(rows > 0 && dim > 0 && (w2 == nullptr) == (y2 == nullptr), "rmsnorm_pair: bad sizes rows=%d dim=%d", rows, dim);
-  const dim3 grid(rows), block(dim >= 1024 ? 256 : 128);
+  const dim3 grid(rows), block(dim >= 1024 ? (rows <= 64 ? 1024 : 256) : 128);      // (few long rows: more threads a row, fewer trips to memory each)
   if (out_dtype == DT_F32) launch_pdl(32, rmsnorm_pair_kernel<float>, grid, block, (size_t)0, stream, x, add, w1, w2, (float*)y1, (float*)y2, dim, eps);
   else if (out_dtype == DT_BF16) launch_pdl(32, rmsnorm_pair_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, x, add, w1, w2, (__nv_bfloat16*)y1, (__nv_bfloat16*)y2, dim, eps);
   else EL_REFUSE(false, "rmsnorm_pair: unknown dtype code %d", out_dtype);

@@ -360,7 +360,12 @@ extern "C" int edgelm_decay_scan(const float* u, int ldu, int q_off, int k_off, 
   const int warps = (long long)n_seqs * H * ((E + LA_WARPS - 1) / LA_WARPS) >= 2 * 148 ? LA_WARPS : 2;
   const dim3 grid(n_seqs * H, (E + warps - 1) / warps), block(warps * 32);
 #define EL_SCAN(NK, U) launch_pdl(pdl_bit_for_tokens(n_tokens), decay_scan_kernel<NK, U>, dim3(grid), dim3(block), (size_t)(0), stream, u, ldu, q_off, k_off, v_off, decay, state, o, seq_tok0, seq_slot, H, K, E, act)
-  if (K <= 32) EL_SCAN(1, 8);
+  if (n_tokens == n_seqs) {      // one token a sequence: no tokens to look ahead for
+    if (K <= 32) EL_SCAN(1, 1);
+    else if (K <= 64) EL_SCAN(2, 1);
+    else if (K <= 128) EL_SCAN(4, 1);
+    else EL_SCAN(8, 1);
+  } else if (K <= 32) EL_SCAN(1, 8);
   else if (K <= 64) EL_SCAN(2, 8);
   else if (K <= 128) EL_SCAN(4, 4);
   else EL_SCAN(8, 1);

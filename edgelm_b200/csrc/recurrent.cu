@@ -621,7 +621,9 @@ extern "C" int edgelm_gated_group_norm(const float* y, const float* gate, int ld
                                        int n_tokens, int inner, int groups, float eps, int gate_first, int gate_sigmoid, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && inner > 0 && groups > 0 && inner % groups == 0, "gated_group_norm: %d values do not split into %d equal groups", inner, groups);
-  const dim3 grid(n_tokens, groups), block(inner / groups >= 1024 ? 256 : (inner / groups >= 128 ? 128 : 32));
+  // (few rows of many values: a block of 1,024 threads walks a row in a quarter of the trips to memory)
+  const int gs = inner / groups;
+  const dim3 grid(n_tokens, groups), block(gs >= 1024 ? ((long long)n_tokens * groups <= 64 ? 1024 : 256) : (gs >= 128 ? 128 : 32));
   if (out_dtype == DT_F32) launch_pdl(pdl_bit_for_tokens(n_tokens), gated_group_norm_kernel<float>, dim3(grid), dim3(block), (size_t)(0), stream, y, gate, ldg, w, (float*)out, inner, groups, eps, gate_first, gate_sigmoid);
   else if (out_dtype == DT_BF16) launch_pdl(pdl_bit_for_tokens(n_tokens), gated_group_norm_kernel<__nv_bfloat16>, dim3(grid), dim3(block), (size_t)(0), stream, y, gate, ldg, w, (__nv_bfloat16*)out, inner, groups, eps, gate_first, gate_sigmoid);
   else EL_REFUSE(false, "gated_group_norm: unknown dtype code %d", out_dtype);

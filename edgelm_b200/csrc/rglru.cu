@@ -273,9 +273,9 @@ __global__ void clamped_glu_kernel(const float* __restrict__ gu, TO* __restrict_
   pdl_launch_dependents();
   pdl_wait();
   if (x != nullptr)      // the bias of the projection that follows, added to the rows that its residual epilogue adds to
-    for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)blockIdx.x * D + i] += x_bias[i];
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < D; i += gridDim.y * blockDim.x) x[(size_t)blockIdx.x * D + i] += x_bias[i];
   const float* row = gu + (size_t)blockIdx.x * 2 * F;
-  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < F; i += gridDim.y * blockDim.x) {    // (few tokens: several blocks a token)
     float g = row[i] + (bias ? bias[i] : 0.f), v = row[F + i] + (bias ? bias[F + i] : 0.f);
     if (limit > 0.f) {
       g = fminf(g, limit);
@@ -338,7 +338,9 @@ extern "C" int edgelm_clamped_glu(const float* gu, void* mid, int out_dtype, int
                                   const float* bias, float* x, const float* x_bias, int D, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && F > 0 && limit >= 0.f, "clamped_glu: bad sizes");
-  const dim3 grid(n_tokens), block(F >= 1024 ? 256 : 128);
+  // a token's row is a chain of trips to memory when one block walks it: with few tokens a block takes 256 or 512 channels
+  const int per_block = F >= 1024 ? 512 : 256;
+  const dim3 grid(n_tokens, n_tokens <= 64 ? (F + per_block - 1) / per_block : 1), block(F >= 1024 ? 256 : 128);
   const int bit = pdl_bit_for_tokens(n_tokens);
   if (out_dtype == DT_F32) launch_pdl(bit, clamped_glu_kernel<float>, grid, block, (size_t)0, stream, gu, (float*)mid, F, limit, alpha, shift, bias, x, x_bias, D);
   else if (out_dtype == DT_BF16) launch_pdl(bit, clamped_glu_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, gu, (__nv_bfloat16*)mid, F, limit, alpha, shift, bias, x, x_bias, D);
