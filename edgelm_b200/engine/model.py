@@ -133,9 +133,11 @@ class DecoderModel:
         def visit(obj):
             nonlocal total
             for v in vars(obj).values():
-                if isinstance(v, torch.Tensor) and v.is_cuda and v.data_ptr() not in seen:
-                    seen.add(v.data_ptr())
-                    total += v.numel() * v.element_size()
+                if isinstance(v, torch.Tensor) and v.is_cuda:
+                    store = v.untyped_storage()           # (views of one stacked tensor count once, as their storage)
+                    if store.data_ptr() not in seen:
+                        seen.add(store.data_ptr())
+                        total += store.nbytes()
                 elif hasattr(v, "weight_shapes") and id(v) not in seen:
                     seen.add(id(v))
                     visit(v)

@@ -72,6 +72,16 @@ class DecayLinearAttention(Part):
     def first_weights(self):
         return (self.w_in,)
 
+    def input_weight(self, view=None):
+        """The weight of this mixer's one product of its input (q | k | v | gate rows); with `view`, keep that tensor instead (a
+        slice of a stack that the caller multiplies once for several mixers, handing the result's columns in as `pre`)."""
+        if view is not None:
+            self.w_in = view
+        return self.w_in
+
+    def input_weight_rows(self):
+        return self.d_in
+
     def fold_out_scale(self, scale, ask=False):
         """Multiply this mixer's output by `scale` from now on (before its weights are loaded): the norm's weight takes it."""
         if not ask:
@@ -94,12 +104,15 @@ class DecayLinearAttention(Part):
                 nbytes((n_tokens, self.hidden), self.dtype) +
                 (nbytes((ops.decay_chunked_scratch_floats(chunks, self.heads, self.d, self.e),), f32) if self._chunked() else 0))
 
-    def forward(self, ctx, h, x, cache, accumulate=True):
+    def forward(self, ctx, h, x, cache, accumulate=True, pre=None):
         h = linear.as_tensor(h)
         T, ws, f32 = h.shape[0], ctx.ws, torch.float32
-        u = ws.alloc((T, self.d_in), f32)
-        with ctx.prof("linear_attn_in_proj"):
-            linear.matmul(ctx, h, self.w_in, u, prefetch=(self.w_o,))
+        if pre is not None:
+            u = pre           # (float32 rows [T, d_in] of any pitch: the product is done)
+        else:
+            u = ws.alloc((T, self.d_in), f32)
+            with ctx.prof("linear_attn_in_proj"):
+                linear.matmul(ctx, h, self.w_in, u, prefetch=(self.w_o,))
         o = ws.alloc((T, self.inner), f32)
         if not ctx.all_single and T >= 8 * ctx.n_seqs and self._chunked():
             tiles = ctx.tiles(ops.DECAY_CHUNK)

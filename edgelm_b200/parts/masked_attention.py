@@ -148,6 +148,16 @@ class MaskedAttention(Part):
         self.lam = 0.0
         self.out_scale = 1.0
 
+    def input_weight(self, view=None):
+        """The weight of this mixer's one product of its input (q | k | v | gate rows); with `view`, keep that tensor instead (a
+        slice of a stack that the caller multiplies once for several mixers, handing the result's columns in as `pre`)."""
+        if view is not None:
+            self.w_qkv = view
+        return self.w_qkv
+
+    def input_weight_rows(self):
+        return self.d_in
+
     def fold_out_scale(self, scale, ask=False):
         """Multiply this mixer's output by `scale` from now on (before its weights are loaded), if that costs nothing: the output
         is linear in the values, and with a convolution on them the values' taps take the constant.  False: it cannot."""
@@ -247,12 +257,15 @@ class MaskedAttention(Part):
                 (nbytes((n_tokens, self.nh * self.dv), self.dtype) if self.diff else 0) + nbytes((n_tokens, self.hidden), self.dtype) +
                 splits_room(n_seqs, self.nh * self.maps, self.dv))
 
-    def forward(self, ctx, h, x, cache, accumulate=True):
+    def forward(self, ctx, h, x, cache, accumulate=True, pre=None):
         h = linear.as_tensor(h)
         T, ws = h.shape[0], ctx.ws
-        u = ws.alloc((T, self.d_in), torch.float32)
-        with ctx.prof("qkv_proj"):
-            linear.matmul(ctx, h, self.w_qkv, u, prefetch=(self.w_o,))
+        if pre is not None:
+            u = pre           # (float32 rows [T, d_in] of any pitch: the product is done)
+        else:
+            u = ws.alloc((T, self.d_in), torch.float32)
+            with ctx.prof("qkv_proj"):
+                linear.matmul(ctx, h, self.w_qkv, u, prefetch=(self.w_o,))
         qkv = u[:, :self.d_qkv]
         gate = u[:, self.d_qkv:] if self.head_gate else None
         bias = self.b_qkv
