@@ -71,7 +71,15 @@ CFG_C = {"architecture": "Radupel", "vocab": 120, "width": 48, "norm": {"eps": 1
     layer(left(16, 2, 8, 12, 2, {"base": 300.0, "dims": 6}, 0.45), right(2, 12, 20, (0.96, 0.88)), 0.7, 1.3, None),
     layer(left(1, 1, 40, 40, 3, None, 0.15), right(1, 72, 8, (0.97,)), 1.5, 0.6, dense(64)),
 ]}
-CONFIGS = {"a": CFG_A, "b": CFG_B, "c": CFG_C}
+# head sizes that the tensor-core kernels take (softmax attention with key = value heads of 64 and 32, in bfloat16) and that the
+# chunked linear attention reads 16 bytes at a time
+CFG_D = {"architecture": "Radupel", "vocab": 150, "width": 64, "norm": {"eps": 1e-5}, "logit_softcap": 20.0,
+         "loop": {"start": 1, "stop": 2, "times": 2}, "layers": [
+    layer(left(4, 2, 64, 64, 3, {"base": 4000.0, "dims": 16}, 0.12), right(2, 64, 64, (0.92, 0.99)), 1.1, 0.9, dense(48)),
+    layer(left(2, 2, 32, 32, 2, {"base": 100.0, "dims": 32}, 0.2), right(1, 32, 64, (0.97,)), 0.9, 1.2,
+          moe(16, 1.1, 4, 2, 2, 2, 1, 1.4, (16, 0.9))),
+]}
+CONFIGS = {"a": CFG_A, "b": CFG_B, "c": CFG_C, "d": CFG_D}
 NEGATIVE_CORRECTIONS = ("c",)      # models whose corrections make every choice score negative
 
 

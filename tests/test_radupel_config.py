@@ -15,7 +15,7 @@ from edgelm_b200.engine.model import DecoderModel
 from edgelm_b200.parts import KVNeed, StateNeed
 
 
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_plan_names_every_tensor_with_its_shape(name):
     cfg = M.CONFIGS[name]
     conf = config_class_for(cfg).from_dict(cfg)

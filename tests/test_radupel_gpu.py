@@ -161,6 +161,36 @@ def test_steps_cut_by_the_engine(dirs, oracles, name):
     eng.check_device_errors()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_head_sizes_of_the_tensor_core_kernels(tmp_path, dtype):
+    """A model whose softmax attention has key = value heads of 64 and 32: in bfloat16 its prompt steps take the tensor-core
+    kernel with float32 scores and weights (prompts of several pages, pieces that go on from cached tokens, unequal batches),
+    its single tokens the CUDA-core kernels, and both must agree with the plain implementation as the float32 model does."""
+    from edgelm_b200.engine.engine import Engine, StepEntry
+    cfg = M.CONFIGS["d"]
+    d = M.write_dir(str(tmp_path / "d"), cfg, 61)
+    pcfg, PW = plain.load(d)
+    eng = Engine.from_dir(d, dtype=dtype, max_tokens=1536)
+    for i, n in enumerate((1, 2, 63, 64, 65, 130, 300)):
+        toks = M.tokens(cfg, n, 100 + i)
+        close(H.run_whole(eng, toks), plain.forward(pcfg, PW, toks), dtype, n)
+    toks = M.tokens(cfg, 260, 110)
+    want = plain.forward(pcfg, PW, toks)
+    close(H.run_tail_one_by_one(eng, toks, 70), want, dtype, "tail 70")
+    slot = eng.open(1)[0]
+    rows, at = [], 0
+    for c in (70, 1, 2, 64, 123):
+        rows.append(eng.step([StepEntry(slot, toks[at:at + c], list(range(c)))]).cpu().numpy())
+        at += c
+    eng.close([slot])
+    close(np.concatenate(rows, 0), want, dtype, "pieces")
+    requests = [M.tokens(cfg, n, 120 + i) for i, n in enumerate((150, 31, 1, 97))]
+    for r, g in zip(requests, H.run_batches(eng, requests, batch_size=4, decode_tail=20)):
+        close(g, plain.forward(pcfg, PW, r), dtype, len(r))
+    eng.cache.check()
+    eng.check_device_errors()
+
+
 def test_a_far_key_decides(tmp_path):
     """Softmax attention whose score scale is raised so that most tokens' softmax rests on one key, often hundreds of tokens
     back, with the linear attention's share turned down: a key lost at a page border, a tail of the convolution dropped
